@@ -1,0 +1,458 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200: one JSON line per run.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl b200|reference]
+
+Headline workload (default): HGEMM, row-major, A not transposed, B transposed, M = N = K = 8192, alpha 1, beta 0,
+A and B ~ 0.1*N(0,1) in fp16, C poisoned with NaN. A step is one clblast::Gemm call through the C ABI.
+With N > 1 GPUs (one process per GPU under torchrun) the problem grows with N (weak scaling): C is M = 8192*N rows,
+each rank owns the 8192 rows of A and C of its block and needs all of B, which rank 0 broadcasts over NCCL inside
+every timed step before the local GEMM. `value` is TFLOPS = 2*M*N*K / t over all ranks, t the max over ranks of the
+device time measured with CUDA events. `e2e` repeats the measurement through the host-synchronous API with pinned
+host buffers: host->device copies of the inputs and the device->host copy of C are inside the timed region.
+
+`--impl reference` times the CPU restatement of the reference's kernels (the oracle port; the reference itself has
+no CPU path without an OpenCL runtime) on a bounded sample of the same workload, on all host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROW, COL, NO, YES = 101, 102, 111, 112
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+# name -> description of one step. kind: gemm | strided | conv
+WORKLOADS = {
+    "hgemm_8192": dict(kind="gemm", precision=16, layout=ROW, ta=NO, tb=YES, m=8192, n=8192, k=8192, alpha=1.0,
+                       beta=0.0, dist="normal0.1", bound="tensor"),
+    "hgemm_16384x4096x8192": dict(kind="gemm", precision=16, layout=ROW, ta=NO, tb=YES, m=16384, n=4096, k=8192,
+                                  alpha=1.0, beta=0.0, dist="normal0.1", bound="tensor"),
+    "sgemm_8192": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=8192, n=8192, k=8192, alpha=1.5,
+                       beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
+    "sgemm_4096": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=4096, n=4096, k=4096, alpha=1.5,
+                       beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
+    "sgemm_1024": dict(kind="gemm", precision=32, layout=ROW, ta=NO, tb=NO, m=1024, n=1024, k=1024, alpha=0.7,
+                       beta=0.3, dist="uniform1", bound="fp32"),
+    "sgemm_ragged": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=4097, n=3071, k=1025, alpha=1.5,
+                         beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
+    "dgemm_8192": dict(kind="gemm", precision=64, layout=COL, ta=NO, tb=NO, m=8192, n=8192, k=8192, alpha=1.0,
+                       beta=0.0, dist="uniform1", bound="fp64"),
+    "batched_32": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=32, n=32, k=32, batch=8192,
+                       alpha=1.0, beta=1.0, dist="uniform1", bound="hbm"),
+    "batched_64x128x96": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=64, n=128, k=96, batch=2048,
+                              alpha=1.0, beta=1.0, dist="uniform1", bound="hbm"),
+    "conv_56": dict(kind="conv", precision=32, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
+                    num_kernels=128, batch=32, bound="fp32"),
+}
+TORCH_DT = {16: "float16", 32: "float32", 64: "float64"}
+ELEM = {16: 2, 32: 4, 64: 8}
+
+
+def flops_of(w, scale_m=1):
+    if w["kind"] == "gemm":
+        return 2.0 * w["m"] * scale_m * w["n"] * w["k"]
+    if w["kind"] == "strided":
+        return 2.0 * w["m"] * w["n"] * w["k"] * w["batch"] * scale_m
+    oh = (w["height"] + 2 * w["pad"] - w["dil"] * (w["kh"] - 1) - 1) // w["stride"] + 1
+    ow = (w["width"] + 2 * w["pad"] - w["dil"] * (w["kw"] - 1) - 1) // w["stride"] + 1
+    return 2.0 * w["batch"] * scale_m * oh * ow * w["num_kernels"] * w["channels"] * w["kh"] * w["kw"]
+
+
+def min_bytes_of(w):
+    """Algorithmic bytes of one launch: every operand read once, C written once (and read once when beta != 0)."""
+    e = ELEM[w["precision"]]
+    if w["kind"] == "gemm":
+        m, n, k = w["m"], w["n"], w["k"]
+        return e * (m * k + k * n + m * n * (2 if w["beta"] != 0 else 1))
+    if w["kind"] == "strided":
+        m, n, k, b = w["m"], w["n"], w["k"], w["batch"]
+        return e * b * (m * k + k * n + m * n * (2 if w["beta"] != 0 else 1))
+    oh = (w["height"] + 2 * w["pad"] - w["dil"] * (w["kh"] - 1) - 1) // w["stride"] + 1
+    ow = (w["width"] + 2 * w["pad"] - w["dil"] * (w["kw"] - 1) - 1) // w["stride"] + 1
+    return e * (w["batch"] * w["channels"] * w["height"] * w["width"] + w["num_kernels"] * w["channels"] * w["kh"] * w["kw"]
+                + w["batch"] * w["num_kernels"] * oh * ow)
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(torch, w, device, seed, rows_scale=1):
+    """Device tensors for one workload, generated on the device from a seed. rows_scale multiplies M (gemm only)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    dt = getattr(torch, TORCH_DT[w["precision"]])
+
+    def fill(n):
+        if w.get("dist") == "normal0.1":
+            return (torch.randn(n, generator=g, device=device, dtype=torch.float32) * 0.1).to(dt)
+        return (torch.rand(n, generator=g, device=device, dtype=torch.float32) * 2 - 1).to(dt)
+
+    if w["kind"] == "gemm":
+        m, n, k = w["m"] * rows_scale, w["n"], w["k"]
+        pad = w.get("ld_pad", 0)
+        a_one, a_two = ((k, m) if w["ta"] == NO else (m, k)) if w["layout"] == ROW else ((m, k) if w["ta"] == NO else (k, m))
+        b_one, b_two = ((n, k) if w["tb"] == NO else (k, n)) if w["layout"] == ROW else ((k, n) if w["tb"] == NO else (n, k))
+        c_one, c_two = (n, m) if w["layout"] == ROW else (m, n)
+        geo = dict(a_ld=a_one + pad, b_ld=b_one + pad, c_ld=c_one + pad)
+        a = fill(geo["a_ld"] * a_two)
+        b = fill(geo["b_ld"] * b_two)
+        c = fill(geo["c_ld"] * c_two) if w["beta"] != 0 else torch.full((geo["c_ld"] * c_two,), float("nan"), device=device, dtype=dt)
+        return dict(a=a, b=b, c=c, **geo)
+    if w["kind"] == "strided":
+        m, n, k, bt = w["m"], w["n"], w["k"], w["batch"] * rows_scale
+        return dict(a=fill(bt * m * k), b=fill(bt * k * n), c=fill(bt * m * n), batch=bt)
+    bt = w["batch"] * rows_scale
+    oh = (w["height"] + 2 * w["pad"] - w["dil"] * (w["kh"] - 1) - 1) // w["stride"] + 1
+    ow = (w["width"] + 2 * w["pad"] - w["dil"] * (w["kw"] - 1) - 1) // w["stride"] + 1
+    im = fill(bt * w["channels"] * w["height"] * w["width"])
+    ker = (torch.randn(w["num_kernels"] * w["channels"] * w["kh"] * w["kw"], generator=g, device=device) * 0.05).to(dt)
+    res = torch.full((bt * w["num_kernels"] * oh * ow,), float("nan"), device=device, dtype=dt)
+    return dict(a=im, b=ker, c=res, batch=bt)
+
+
+def launch(cb, w, t, stream, m_override=None):
+    """One step of the workload on `stream` (None = the reference's host-synchronous semantics)."""
+    if w["kind"] == "gemm":
+        m = m_override or w["m"]
+        return cb.Gemm(w["layout"], w["ta"], w["tb"], m, w["n"], w["k"], w["alpha"], t["a"], 0, t["a_ld"], t["b"], 0,
+                       t["b_ld"], w["beta"], t["c"], 0, t["c_ld"], stream=stream)
+    if w["kind"] == "strided":
+        m, n, k = w["m"], w["n"], w["k"]
+        return cb.GemmStridedBatched(w["layout"], w["ta"], w["tb"], m, n, k, w["alpha"], t["a"], 0, m, m * k, t["b"], 0,
+                                     k, k * n, w["beta"], t["c"], 0, m, m * n, t["batch"], stream=stream)
+    return cb.Convgemm(151, w["channels"], w["height"], w["width"], w["kh"], w["kw"], w["pad"], w["pad"], w["stride"],
+                       w["stride"], w["dil"], w["dil"], w["num_kernels"], t["batch"], t["a"], 0, t["b"], 0, t["c"], 0,
+                       stream=stream)
+
+
+def time_steps(torch, fn, steps, warmup, dist=None):
+    """Warm-up, then exactly `steps` calls bracketed by barrier + synchronize; returns the max-over-ranks ms."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = start.elapsed_time(end)
+    if dist is not None:
+        tms = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    return ms
+
+
+# ---- CPU legs (the only place the oracle is executed outside tests) ----------------------------------------
+
+def cpu_sample(w, seconds_target=12.0):
+    """Times the oracle port on a bounded sample of the workload. Returns (tflops, cores, description)."""
+    from oracle import cpu_oracle as oracle
+    oracle.build()
+    cores = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    p = w["precision"]
+    dt = oracle.NP_OF[p]
+    if w["kind"] == "gemm":
+        n, k = w["n"], w["k"]
+        # a block of rows of C with the full N and K: same inner loops, bounded work
+        rate_guess = {16: 3e9, 32: 30e9, 64: 15e9}[p] * max(1, cores // 8)
+        rows = int(max(8, min(w["m"], seconds_target * rate_guess / (2.0 * n * k))))
+        a = rng.uniform(-1, 1, rows * k).astype(dt)
+        b = rng.uniform(-1, 1, n * k).astype(dt)
+        c = np.zeros(rows * n, dtype=dt)
+        # row-major NoTrans/Trans geometry for the headline; other GEMM workloads use the same sample geometry
+        t0 = time.perf_counter()
+        oracle.gemm(p, ROW, NO, YES, rows, n, k, w["alpha"], a, 0, k, b, 0, k, 0.0, c, 0, n)
+        dtm = time.perf_counter() - t0
+        return 2.0 * rows * n * k / dtm / 1e12, cores, f"{rows} of {w['m']} rows of C (full N={n}, K={k}), type-T reference order, {dtm:.1f} s"
+    if w["kind"] == "strided":
+        m, n, k = w["m"], w["n"], w["k"]
+        nb = w["batch"]
+        a = rng.uniform(-1, 1, nb * m * k).astype(dt)
+        b = rng.uniform(-1, 1, nb * k * n).astype(dt)
+        c = rng.uniform(-1, 1, nb * m * n).astype(dt)
+        t0 = time.perf_counter()
+        for i in range(nb):
+            oracle.gemm(p, COL, NO, NO, m, n, k, 1.0, a, i * m * k, m, b, i * k * n, k, 1.0, c, i * m * n, m)
+        dtm = time.perf_counter() - t0
+        return 2.0 * nb * m * n * k / dtm / 1e12, cores, f"{nb} of {w['batch']} batches, {dtm:.1f} s"
+    nb = min(w["batch"], 32)
+    im = rng.uniform(-1, 1, nb * w["channels"] * w["height"] * w["width"]).astype(dt)
+    ker = (rng.standard_normal(w["num_kernels"] * w["channels"] * w["kh"] * w["kw"]) * 0.05).astype(dt)
+    oh, ow = oracle.conv_output_size(w["height"], w["width"], w["kh"], w["kw"], w["pad"], w["pad"], w["stride"],
+                                     w["stride"], w["dil"], w["dil"])
+    res = np.zeros(nb * w["num_kernels"] * oh * ow, dtype=dt)
+    t0 = time.perf_counter()
+    oracle.convgemm(p, 151, w["channels"], w["height"], w["width"], w["kh"], w["kw"], w["pad"], w["pad"], w["stride"],
+                    w["stride"], w["dil"], w["dil"], w["num_kernels"], nb, im, 0, ker, 0, res, 0)
+    dtm = time.perf_counter() - t0
+    return flops_of(w) / w["batch"] * nb / dtm / 1e12, cores, f"{nb} of {w['batch']} images, {dtm:.1f} s"
+
+
+def run_reference_arm(args, w, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    sample = ""
+    cores = 1
+    for i in range(args.warmup + args.steps):
+        v, cores, sample = cpu_sample(w, seconds_target=3.0)
+        if i >= args.warmup:
+            vals.append(v)
+    value = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": {16: "f16", 32: "f32", 64: "f64"}[w["precision"]], "data": "synthetic",
+            "config": {"workload": name},
+            "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm ------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="hgemm_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--no-sweep", action="store_true", help="skip the short per-config sweep added at N=1")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    w = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+        return
+
+    import torch
+    import clblast_b200 as cb
+    cb.lib()  # fail loudly when the native library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); nothing is computed on the host")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as tdist
+        tdist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = tdist
+    if args.gpus != world and rank == 0:
+        print(f"note: --gpus {args.gpus} but WORLD_SIZE is {world}; using {world}", file=sys.stderr)
+    n_gpus = world
+    device = torch.device("cuda", local_rank)
+    peaks, peak_kind = load_peaks()
+
+    # Per-rank problem: every rank owns one full copy of the workload's M rows (weak scaling); for the GEMM
+    # workloads rank 0's B is the one everybody uses and is re-broadcast inside every step.
+    t = make_inputs(torch, w, device, seed=1234 + rank)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        if dist is not None and w["kind"] == "gemm":
+            dist.broadcast(t["b"], src=0)
+        st = launch(cb, w, t, stream)
+        if st != 0:
+            raise RuntimeError(f"library call failed with status {st}")
+
+    sampler = ClockSampler(local_rank)
+    step()
+    torch.cuda.synchronize()
+    kernel_name = cb.last_kernel()
+    launches_before = None
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler.start()
+    launches_before = cb.launch_count()
+    ms = time_steps(torch, step, args.steps, 0, dist)
+    launches = cb.launch_count() - launches_before
+    clocks = sampler.stop()
+
+    total_flops = flops_of(w) * n_gpus
+    ms_per_step = ms / args.steps
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # Dominant kernel alone (no collective), CUDA events on the launching stream: the roofline numerator.
+    def kernel_only():
+        launch(cb, w, t, stream)
+    kms = time_steps(torch, kernel_only, args.steps, 3, None) / args.steps
+    bound = w["bound"]
+    if bound == "hbm":
+        achieved = min_bytes_of(w) / (kms * 1e-3) / 1e9
+        peak = float(peaks["hbm_gbs"])
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": f"{peak_kind} STREAM-style copy"}
+    else:
+        achieved = flops_of(w) / (kms * 1e-3) / 1e12
+        if bound == "tensor":
+            peak = float(peaks["bf16_tflops"])
+            src = f"{peak_kind} cuBLAS bf16 burst"
+        elif bound == "fp32":
+            peak = 148 * 128 * 2 * 1.965e9 / 1e12  # FFMA lanes x 2 flop x max SM clock
+            src = "nominal FP32 FFMA pipe at 1965 MHz (no measured fp32 entry)"
+        else:
+            peak = 148 * 64 * 2 * 1.965e9 / 1e12
+            src = "nominal FP64 DFMA pipe at 1965 MHz (no measured fp64 entry)"
+        roof = {"bound": "tensor" if bound == "tensor" else bound, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None, "peak_source": src}
+    roof["kernel"] = kernel_name
+    roof["kernel_ms"] = kms
+    roof["algorithmic_bytes"] = min_bytes_of(w)
+
+    # End to end through the host-synchronous API with pinned host buffers.
+    host = {k: torch.empty(t[k].shape, dtype=t[k].dtype).pin_memory() for k in ("a", "b", "c")}
+    for k in ("a", "b", "c"):
+        host[k].copy_(t[k])
+    h2d = host["a"].numel() * host["a"].element_size()
+    if dist is None or rank == 0 or w["kind"] != "gemm":
+        h2d += host["b"].numel() * host["b"].element_size()
+    needs_c_in = w.get("beta", 0.0) != 0
+    if needs_c_in:
+        h2d += host["c"].numel() * host["c"].element_size()
+    d2h = host["c"].numel() * host["c"].element_size()
+
+    def e2e_step():
+        t["a"].copy_(host["a"], non_blocking=True)
+        if dist is None or rank == 0 or w["kind"] != "gemm":
+            t["b"].copy_(host["b"], non_blocking=True)
+        if needs_c_in:
+            t["c"].copy_(host["c"], non_blocking=True)
+        if dist is not None and w["kind"] == "gemm":
+            dist.broadcast(t["b"], src=0)
+        torch.cuda.current_stream().synchronize()  # the library's private stream does not order against ours
+        st = launch(cb, w, t, None)
+        if st != 0:
+            raise RuntimeError(f"library call failed with status {st}")
+        host["c"].copy_(t["c"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = time_steps(torch, e2e_step, e2e_steps, 2, dist) / e2e_steps
+    e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
+
+    line = {
+        "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": n_gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": {16: "f16", 32: "f32", 64: "f64"}[w["precision"]], "data": "synthetic",
+        "config": {"workload": args.workload, **{k: v for k, v in w.items() if k not in ("kind", "bound")},
+                   "per_gpu": "one full copy of the workload per GPU; B broadcast from rank 0 every step" if n_gpus > 1
+                   else "single GPU", "l2": "inputs larger than L2 (no flush needed)" if min_bytes_of(w) > 126e6
+                   else "working set fits in L2; no flush between iterations"},
+        "roofline": roof,
+        "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+
+    if rank == 0 and n_gpus == 1 and not args.no_sweep:
+        sweep = {}
+        for name, ww in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            try:
+                tt = make_inputs(torch, ww, device, seed=99)
+                fn = lambda: launch(cb, ww, tt, stream)
+                ms_w = time_steps(torch, fn, 5, 3, None) / 5
+                sweep[name] = {"tflops": flops_of(ww) / (ms_w * 1e-3) / 1e12, "ms": ms_w,
+                               "gbs": min_bytes_of(ww) / (ms_w * 1e-3) / 1e9, "kernel": cb.last_kernel()}
+                del tt
+                torch.cuda.empty_cache()
+            except Exception as exc:  # a sweep entry must never take the headline down
+                sweep[name] = {"error": str(exc)}
+        line["sweep"] = sweep
+
+    if rank == 0 and n_gpus == 1 and not args.no_cpu:
+        v, cores, sample = cpu_sample(w)
+        line["cpu_baseline"] = {"value": v, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": sample}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

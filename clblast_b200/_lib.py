@@ -1,0 +1,62 @@
+"""ctypes binding of libclblast.so's C ABI (include/b200blas.h)."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_size_t, c_uint64, c_void_p, POINTER
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libclblast.so"
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    """libclblast.so has not been built; there is no fallback path."""
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library once. Raises LibraryMissing when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise LibraryMissing(f"{LIB_PATH} not found: run `python -m clblast_b200.build` (needs nvcc). "
+                             "This package has no CPU or PyTorch fallback.")
+    L = ctypes.CDLL(str(LIB_PATH))
+    sz, vp, i = c_size_t, c_void_p, c_int
+    L.b200blas_gemm.restype = i
+    L.b200blas_gemm.argtypes = [i, i, i, i, sz, sz, sz, vp, vp, sz, sz, vp, sz, sz, vp, vp, sz, sz, vp, i]
+    L.b200blas_gemm_strided_batched.restype = i
+    L.b200blas_gemm_strided_batched.argtypes = [i, i, i, i, sz, sz, sz, vp, vp, sz, sz, sz, vp, sz, sz, sz, vp, vp, sz,
+                                                sz, sz, sz, vp, i]
+    L.b200blas_gemm_batched.restype = i
+    L.b200blas_gemm_batched.argtypes = [i, i, i, i, sz, sz, sz, vp, vp, POINTER(sz), sz, vp, POINTER(sz), sz, vp, vp,
+                                        POINTER(sz), sz, sz, vp, i]
+    L.b200blas_convgemm.restype = i
+    L.b200blas_convgemm.argtypes = [i, i] + [sz] * 13 + [vp, sz, vp, sz, vp, sz, vp, i]
+    L.b200blas_gemm_temp_buffer_size.restype = i
+    L.b200blas_gemm_temp_buffer_size.argtypes = [i, i, i, i] + [sz] * 9 + [POINTER(sz)]
+    L.b200blas_clear_cache.restype = i
+    L.b200blas_clear_cache.argtypes = []
+    L.b200blas_fill_cache.restype = i
+    L.b200blas_fill_cache.argtypes = [i]
+    L.b200blas_override_parameters.restype = i
+    L.b200blas_override_parameters.argtypes = [i, c_char_p, i, POINTER(c_char_p), POINTER(sz), sz]
+    L.b200blas_retrieve_parameters.restype = i
+    L.b200blas_retrieve_parameters.argtypes = [i, c_char_p, i, POINTER(c_char_p), POINTER(sz), sz, POINTER(sz)]
+    L.b200blas_last_kernel.restype = c_char_p
+    L.b200blas_last_kernel.argtypes = []
+    L.b200blas_launch_count.restype = c_uint64
+    L.b200blas_launch_count.argtypes = []
+    L.b200blas_version.restype = c_char_p
+    L.b200blas_version.argtypes = []
+    _lib = L
+    return L
+
+
+# Every symbol include/b200blas.h declares; tests check that the built library exports all of them.
+C_ABI_SYMBOLS = [
+    "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_convgemm",
+    "b200blas_gemm_temp_buffer_size", "b200blas_clear_cache", "b200blas_fill_cache", "b200blas_override_parameters",
+    "b200blas_retrieve_parameters", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
+]

@@ -1,0 +1,226 @@
+"""Python mirror of the reference's CUDA API for the GEMM family, over the library's C ABI.
+
+Function names, argument order and meaning and the returned status codes are those of the reference's
+``include/clblast_cuda.h`` (Gemm :385-390, Convgemm :486-493, GemmBatched :502-507, GemmStridedBatched :511-518,
+GemmTempBufferSize :523-527, cache and parameter calls :533-550), so the parity tests read like the reference's own
+test descriptors (``test/routines/level3/xgemm.hpp:115-121``). Buffers are device pointers (``int``) or CUDA
+``torch.Tensor`` objects; the element type comes from ``precision`` or, for tensors, from the tensor's dtype.
+``context``/``device`` of the C++ signature are implicit: the calling thread's current CUDA context is used.
+
+Every call returns a :class:`StatusCode` value; nothing is computed on the host, and a missing library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import struct
+from typing import Sequence
+
+import numpy as np
+
+from ._lib import lib
+
+
+class StatusCode(enum.IntEnum):
+    kSuccess = 0
+    kNotImplemented = -1024
+    kInvalidMatrixA = -1022
+    kInvalidMatrixB = -1021
+    kInvalidMatrixC = -1020
+    kInvalidDimension = -1017
+    kInvalidLeadDimA = -1016
+    kInvalidLeadDimB = -1015
+    kInvalidLeadDimC = -1014
+    kInsufficientMemoryA = -1011
+    kInsufficientMemoryB = -1010
+    kInsufficientMemoryC = -1009
+    kInsufficientMemoryTemp = -2050
+    kInvalidBatchCount = -2049
+    kInvalidOverrideKernel = -2048
+    kMissingOverrideParameter = -2047
+    kNoHalfPrecision = -2045
+    kNoDoublePrecision = -2044
+    kDatabaseError = -2041
+    kUnknownError = -2040
+    kUnexpectedError = -2039
+
+
+class Layout(enum.IntEnum):
+    kRowMajor = 101
+    kColMajor = 102
+
+
+class Transpose(enum.IntEnum):
+    kNo = 111
+    kYes = 112
+    kConjugate = 113
+
+
+class KernelMode(enum.IntEnum):
+    kCrossCorrelation = 151
+    kConvolution = 152
+
+
+class Precision(enum.IntEnum):
+    kHalf = 16
+    kSingle = 32
+    kDouble = 64
+    kComplexSingle = 3232
+    kComplexDouble = 6464
+
+
+_NP_OF = {16: np.float16, 32: np.float32, 64: np.float64, 3232: np.complex64, 6464: np.complex128}
+
+
+def precision_of(buf, precision=None) -> int:
+    """Precision code of a buffer: explicit, or inferred from a torch tensor's dtype."""
+    if precision is not None:
+        return int(precision)
+    import torch
+    table = {torch.float16: 16, torch.float32: 32, torch.float64: 64, torch.complex64: 3232, torch.complex128: 6464}
+    if not hasattr(buf, "dtype") or buf.dtype not in table:
+        raise TypeError("pass precision= for raw pointers or unsupported tensor dtypes")
+    return table[buf.dtype]
+
+
+def _ptr(buf) -> int:
+    if buf is None:
+        return 0
+    if isinstance(buf, int):
+        return buf
+    if hasattr(buf, "data_ptr"):
+        if not buf.is_cuda:
+            raise ValueError("buffers must live in device memory")
+        return buf.data_ptr()
+    raise TypeError(f"unsupported buffer type {type(buf)}")
+
+
+def scalar_bytes(precision: int, value) -> ctypes.Array:
+    """One host scalar of the given precision, laid out as the C ABI expects."""
+    if precision == 16:
+        raw = np.float16(value).tobytes()
+    elif precision in (32, 64):
+        raw = _NP_OF[precision](value).tobytes()
+    else:
+        raw = _NP_OF[precision](complex(value)).tobytes()
+    return ctypes.create_string_buffer(raw, len(raw))
+
+
+def _stream_arg(stream):
+    """(pointer, async flag): stream=None reproduces the reference's host-synchronous call."""
+    if stream is None:
+        return None, 0
+    if isinstance(stream, int):
+        return ctypes.c_void_p(stream), 1
+    return ctypes.c_void_p(stream.cuda_stream), 1
+
+
+def _status(code: int):
+    try:
+        return StatusCode(code)
+    except ValueError:
+        return code  # positive values are raw CUDA error numbers
+
+
+def Gemm(layout, a_transpose, b_transpose, m, n, k, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta,
+         c_buffer, c_offset, c_ld, *, precision=None, stream=None):
+    """C = alpha*op(A)*op(B) + beta*C (reference: clblast::Gemm, include/clblast_cuda.h:385-390)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_gemm(p, int(layout), int(a_transpose), int(b_transpose), m, n, k,
+                                       scalar_bytes(p, alpha), _ptr(a_buffer), a_offset, a_ld, _ptr(b_buffer),
+                                       b_offset, b_ld, scalar_bytes(p, beta), _ptr(c_buffer), c_offset, c_ld, sp,
+                                       is_async))
+
+
+def GemmStridedBatched(layout, a_transpose, b_transpose, m, n, k, alpha, a_buffer, a_offset, a_ld, a_stride, b_buffer,
+                       b_offset, b_ld, b_stride, beta, c_buffer, c_offset, c_ld, c_stride, batch_count, *,
+                       precision=None, stream=None):
+    """Batch b uses offset + b*stride (reference: clblast::GemmStridedBatched, include/clblast_cuda.h:511-518)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_gemm_strided_batched(
+        p, int(layout), int(a_transpose), int(b_transpose), m, n, k, scalar_bytes(p, alpha), _ptr(a_buffer), a_offset,
+        a_ld, a_stride, _ptr(b_buffer), b_offset, b_ld, b_stride, scalar_bytes(p, beta), _ptr(c_buffer), c_offset,
+        c_ld, c_stride, batch_count, sp, is_async))
+
+
+def GemmBatched(layout, a_transpose, b_transpose, m, n, k, alphas: Sequence, a_buffer, a_offsets: Sequence[int], a_ld,
+                b_buffer, b_offsets: Sequence[int], b_ld, betas: Sequence, c_buffer, c_offsets: Sequence[int], c_ld,
+                batch_count, *, precision=None, stream=None):
+    """Per-batch scalars and offsets are host sequences (reference: clblast::GemmBatched, clblast_cuda.h:502-507)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    npdt = _NP_OF[p]
+    al = np.ascontiguousarray(np.asarray(alphas, dtype=npdt))
+    be = np.ascontiguousarray(np.asarray(betas, dtype=npdt))
+    if len(al) != batch_count or len(be) != batch_count or len(a_offsets) != batch_count or \
+            len(b_offsets) != batch_count or len(c_offsets) != batch_count:
+        return StatusCode.kInvalidBatchCount  # the reference checks the vector lengths (xgemmbatched.cpp:70-73)
+    arr = ctypes.c_size_t * max(batch_count, 1)
+    ao, bo, co = arr(*a_offsets), arr(*b_offsets), arr(*c_offsets)
+    return _status(lib().b200blas_gemm_batched(
+        p, int(layout), int(a_transpose), int(b_transpose), m, n, k, al.ctypes.data_as(ctypes.c_void_p),
+        _ptr(a_buffer), ao, a_ld, _ptr(b_buffer), bo, b_ld, be.ctypes.data_as(ctypes.c_void_p), _ptr(c_buffer), co,
+        c_ld, batch_count, sp, is_async))
+
+
+def Convgemm(kernel_mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dilation_h,
+             dilation_w, num_kernels, batch_count, im_buffer, im_offset, kernel_buffer, kernel_offset, result_buffer,
+             result_offset, *, precision=None, stream=None):
+    """Batched NCHW convolution (reference: clblast::Convgemm, include/clblast_cuda.h:486-493)."""
+    p = precision_of(result_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_convgemm(
+        p, int(kernel_mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+        dilation_h, dilation_w, num_kernels, batch_count, _ptr(im_buffer), im_offset, _ptr(kernel_buffer),
+        kernel_offset, _ptr(result_buffer), result_offset, sp, is_async))
+
+
+def GemmTempBufferSize(layout, a_transpose, b_transpose, m, n, k, a_offset, a_ld, b_offset, b_ld, c_offset, c_ld, *,
+                       precision):
+    """(status, bytes) — always 0 bytes here (reference: clblast::GemmTempBufferSize, clblast_cuda.h:523-527)."""
+    out = ctypes.c_size_t(0)
+    st = lib().b200blas_gemm_temp_buffer_size(int(precision), int(layout), int(a_transpose), int(b_transpose), m, n, k,
+                                              a_offset, a_ld, b_offset, b_ld, c_offset, c_ld, ctypes.byref(out))
+    return _status(st), out.value
+
+
+def ClearCache():
+    return _status(lib().b200blas_clear_cache())
+
+
+def FillCache(device: int = 0):
+    return _status(lib().b200blas_fill_cache(device))
+
+
+def OverrideParameters(device: int, kernel_name: str, precision, parameters: dict):
+    names = list(parameters.keys())
+    n = len(names)
+    c_names = (ctypes.c_char_p * max(n, 1))(*[s.encode() for s in names])
+    c_vals = (ctypes.c_size_t * max(n, 1))(*[int(parameters[s]) for s in names])
+    return _status(lib().b200blas_override_parameters(device, kernel_name.encode(), int(precision), c_names, c_vals, n))
+
+
+def RetrieveParameters(device: int, kernel_name: str, precision):
+    """(status, dict) of the family's current parameter values."""
+    count = ctypes.c_size_t(0)
+    st = lib().b200blas_retrieve_parameters(device, kernel_name.encode(), int(precision), None, None, 0,
+                                            ctypes.byref(count))
+    if st != 0:
+        return _status(st), {}
+    n = count.value
+    c_names = (ctypes.c_char_p * n)()
+    c_vals = (ctypes.c_size_t * n)()
+    st = lib().b200blas_retrieve_parameters(device, kernel_name.encode(), int(precision), c_names, c_vals, n,
+                                            ctypes.byref(count))
+    return _status(st), {c_names[i].decode(): c_vals[i] for i in range(n)}
+
+
+def last_kernel() -> str:
+    """Kernel family chosen by the most recent compute call on this thread."""
+    return lib().b200blas_last_kernel().decode()
+
+
+def launch_count() -> int:
+    return int(lib().b200blas_launch_count())

@@ -1,0 +1,31 @@
+#include "driver_api.h"
+
+#include <dlfcn.h>
+
+namespace b200 {
+
+namespace {
+
+DriverApi bind() {
+  DriverApi api = {};
+  void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) return api;
+  auto sym = [&](const char* name) { return dlsym(lib, name); };
+  api.CtxGetCurrent = reinterpret_cast<decltype(api.CtxGetCurrent)>(sym("cuCtxGetCurrent"));
+  api.CtxPushCurrent = reinterpret_cast<decltype(api.CtxPushCurrent)>(sym("cuCtxPushCurrent_v2"));
+  api.CtxPopCurrent = reinterpret_cast<decltype(api.CtxPopCurrent)>(sym("cuCtxPopCurrent_v2"));
+  api.MemGetAddressRange = reinterpret_cast<decltype(api.MemGetAddressRange)>(sym("cuMemGetAddressRange_v2"));
+  api.TensorMapEncodeTiled = reinterpret_cast<decltype(api.TensorMapEncodeTiled)>(sym("cuTensorMapEncodeTiled"));
+  api.ok = api.CtxGetCurrent && api.CtxPushCurrent && api.CtxPopCurrent && api.MemGetAddressRange &&
+           api.TensorMapEncodeTiled;
+  return api;
+}
+
+}  // namespace
+
+const DriverApi& driver_api() {
+  static const DriverApi api = bind();
+  return api;
+}
+
+}  // namespace b200

@@ -1,0 +1,90 @@
+/* C ABI of the B200 GEMM library (libclblast.so).
+ *
+ * One flat extern "C" entry point per routine of CLBlast's GEMM family. The C++ templates of
+ * include/clblast_cuda.h are thin shims over these; other languages bind these directly.
+ * Conventions shared by all entry points:
+ *   - `dtype` is CLBlast's Precision value: 16 (IEEE half), 32, 64, 3232 (complex float), 6464 (complex double).
+ *   - `layout`, `a_transpose`, `b_transpose`, `kernel_mode` are CLBlast's enum values (101/102, 111/112/113, 151/152).
+ *   - matrices are DEVICE pointers; offsets, leading dimensions and strides are in elements of the dtype.
+ *   - scalars are passed by HOST pointer to one element of the dtype (half: a 16-bit pattern; complex: re, im).
+ *   - the return value is CLBlast's StatusCode as an int: 0 success, negative CLBlast codes, positive CUresult.
+ *   - `async == 0` reproduces the reference's semantics: the work runs on a library-owned non-blocking stream
+ *     and the call returns after it completed (`stream` is ignored). `async != 0` enqueues the work on `stream`
+ *     (a CUstream / cudaStream_t, NULL being the default stream) and returns without waiting.
+ *   - nothing is ever computed on the host: if no sm_100 device is usable the call fails with a CUresult.
+ * The caller's CUDA context must be current on the calling thread.
+ */
+#ifndef B200BLAS_H_
+#define B200BLAS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Replaces clblast::Gemm<T> (reference: include/clblast_cuda.h:385-390, src/clblast_cuda.cpp:1158-1178,
+ * host logic src/routines/level3/xgemm.cpp:57-94). */
+int b200blas_gemm(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n, size_t k,
+                  const void* alpha, const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset,
+                  size_t b_ld, const void* beta, void* c, size_t c_offset, size_t c_ld, void* stream, int async);
+
+/* Replaces clblast::GemmStridedBatched<T> (include/clblast_cuda.h:511-518, src/clblast_cuda.cpp:1763-1783,
+ * src/routines/levelx/xgemmstridedbatched.cpp:59-102). */
+int b200blas_gemm_strided_batched(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n,
+                                  size_t k, const void* alpha, const void* a, size_t a_offset, size_t a_ld,
+                                  size_t a_stride, const void* b, size_t b_offset, size_t b_ld, size_t b_stride,
+                                  const void* beta, void* c, size_t c_offset, size_t c_ld, size_t c_stride,
+                                  size_t batch_count, void* stream, int async);
+
+/* Replaces clblast::GemmBatched<T> (include/clblast_cuda.h:502-507, src/clblast_cuda.cpp:1704-1734,
+ * src/routines/levelx/xgemmbatched.cpp:59-112). `alphas`, `betas` and the three offset arrays are HOST arrays
+ * of batch_count entries; the library stages them into device scratch it owns. */
+int b200blas_gemm_batched(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n, size_t k,
+                          const void* alphas, const void* a, const size_t* a_offsets, size_t a_ld, const void* b,
+                          const size_t* b_offsets, size_t b_ld, const void* betas, void* c, const size_t* c_offsets,
+                          size_t c_ld, size_t batch_count, void* stream, int async);
+
+/* Replaces clblast::Convgemm<T> (include/clblast_cuda.h:486-493, src/clblast_cuda.cpp:1625-1645,
+ * src/routines/levelx/xconvgemm.cpp:50-161). dtype 16, 32 or 64. */
+int b200blas_convgemm(int dtype, int kernel_mode, size_t channels, size_t height, size_t width, size_t kernel_h,
+                      size_t kernel_w, size_t pad_h, size_t pad_w, size_t stride_h, size_t stride_w,
+                      size_t dilation_h, size_t dilation_w, size_t num_kernels, size_t batch_count, const void* im,
+                      size_t im_offset, const void* kernel, size_t kernel_offset, void* result, size_t result_offset,
+                      void* stream, int async);
+
+/* Replaces clblast::GemmTempBufferSize<T> (include/clblast_cuda.h:523-527, src/clblast_cuda.cpp:1818-1843).
+ * Validates the dimensions and writes 0: no kernel of this library needs caller scratch. */
+int b200blas_gemm_temp_buffer_size(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n,
+                                   size_t k, size_t a_offset, size_t a_ld, size_t b_offset, size_t b_ld,
+                                   size_t c_offset, size_t c_ld, size_t* temp_buffer_size);
+
+/* Replace clblast::ClearCache / FillCache (include/clblast_cuda.h:533-537, src/api_common.cpp:25-33,120-135). */
+int b200blas_clear_cache(void);
+int b200blas_fill_cache(int device);
+
+/* Replace clblast::OverrideParameters / RetrieveParameters (include/clblast_cuda.h:541-550,
+ * src/api_common.cpp:140-221) with a flat form: `names` is an array of `count` NUL-terminated strings and
+ * `values` the matching numbers. Retrieve writes at most `capacity` entries (names are pointers to storage
+ * owned by the library, valid until the next override of that family) and stores the family's size in *count. */
+int b200blas_override_parameters(int device, const char* kernel_name, int precision, const char* const* names,
+                                 const size_t* values, size_t count);
+int b200blas_retrieve_parameters(int device, const char* kernel_name, int precision, const char** names,
+                                 size_t* values, size_t capacity, size_t* count);
+
+/* Introspection for tests and benchmarks (no counterpart in the reference). */
+
+/* Name of the kernel family the selection table picked for the most recent compute call on this thread,
+ * e.g. "tc_f16_128x256", "simt_128x128", "simt_32x32", "conv_simt". Never NULL. */
+const char* b200blas_last_kernel(void);
+/* Number of kernel launches issued by this library in this process so far. */
+uint64_t b200blas_launch_count(void);
+/* Library version string. */
+const char* b200blas_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200BLAS_H_ */

@@ -1,0 +1,90 @@
+"""Parity of Convgemm against the oracle's restatement of the reference's host convolution
+(test/routines/levelx/xconvgemm.hpp:151-196). Grid after test/correctness/testblas.hpp:146-158: padding {0,1},
+dilation {1,2}, kernel {1,3}, output channels {1,6}, stride {1,3}, input channels {1,2}, both kernel modes."""
+import itertools
+
+import numpy as np
+import pytest
+
+import clblast_b200 as cb
+from oracle import cpu_oracle as oracle
+from tests import harness as H
+
+pytestmark = pytest.mark.gpu
+
+
+def check_conv(torch, rng, precision, mode, channels, height, width, kh, kw, pad, stride, dil, num_kernels, batch,
+               offs=(0, 0, 0), weight_scale=1.0):
+    oh, ow = oracle.conv_output_size(height, width, kh, kw, pad, pad, stride, stride, dil, dil)
+    im = H.rand_buffer(rng, precision, offs[0] + batch * channels * height * width + H.CANARY, -1, 1)
+    ker = (H.rand_buffer(rng, precision, offs[1] + num_kernels * channels * kh * kw + H.CANARY, -1, 1)
+           * np.asarray(weight_scale, dtype=H.NP_OF[precision]))
+    res = H.rand_buffer(rng, precision, offs[2] + batch * num_kernels * oh * ow + H.CANARY, -1, 1)
+    res_in = res.copy()
+    res_in[offs[2]:offs[2] + batch * num_kernels * oh * ow] = np.nan  # beta is 0: the old result must be ignored
+    dim, dker, dres = (H.to_device(torch, precision, x) for x in (im, ker, res_in))
+    torch.cuda.synchronize()
+    st = cb.Convgemm(mode, channels, height, width, kh, kw, pad, pad, stride, stride, dil, dil, num_kernels, batch, dim,
+                     offs[0], dker, offs[1], dres, offs[2], precision=precision)
+    assert st == cb.StatusCode.kSuccess, st
+    got = H.to_host(precision, dres)
+    want = oracle.convgemm(precision, mode, channels, height, width, kh, kw, pad, pad, stride, stride, dil, dil,
+                           num_kernels, batch, im, offs[0], ker, offs[1], res, offs[2], f64=True)
+    mask = np.zeros(res.size, dtype=bool)
+    mask[offs[2]:offs[2] + batch * num_kernels * oh * ow] = True
+    H.check_against_oracle(precision, got, want, mask, res_in)
+    return np.abs(got[mask].astype(np.float64) - want[mask]).max()
+
+
+@pytest.mark.parametrize("precision", (32, 64, 16))
+def test_reference_grid(cuda, precision):
+    rng = np.random.default_rng(42)
+    i = 0
+    for mode, pad, dil, ksz, nk, stride, ch in itertools.product((151, 152), (0, 1), (1, 2), (1, 3), (1, 6), (1, 3),
+                                                                 (1, 2)):
+        hw, batch = ((7, 1), (8, 3), (13, 2))[i % 3]
+        check_conv(cuda, rng, precision, mode, ch, hw, hw + i % 2, ksz, ksz, pad, stride, dil, nk, batch,
+                   offs=(0, 0, 0) if i % 2 else (10, 10, 10))
+        i += 1
+
+
+def test_kernel_larger_than_image_gives_one_output(cuda):
+    rng = np.random.default_rng(1)
+    check_conv(cuda, rng, 32, 151, 2, 2, 2, 3, 3, 0, 1, 2, 3, 2)
+
+
+def test_rectangular_kernel_and_wide_image(cuda):
+    rng = np.random.default_rng(2)
+    for mode in (151, 152):
+        oh, ow = oracle.conv_output_size(20, 33, 3, 5, 1, 1, 2, 2, 1, 1)
+        assert (oh, ow) == (10, 16)
+        im = H.rand_buffer(rng, 32, 2 * 5 * 20 * 33, -1, 1)
+        ker = H.rand_buffer(rng, 32, 7 * 5 * 3 * 5, -1, 1)
+        res = np.zeros(2 * 7 * oh * ow, dtype=np.float32)
+        dim, dker, dres = (H.to_device(cuda, 32, x) for x in (im, ker, res))
+        cuda.cuda.synchronize()
+        assert cb.Convgemm(mode, 5, 20, 33, 3, 5, 1, 1, 2, 2, 1, 1, 7, 2, dim, 0, dker, 0, dres, 0) == 0
+        want = oracle.convgemm(32, mode, 5, 20, 33, 3, 5, 1, 1, 2, 2, 1, 1, 7, 2, im, 0, ker, 0, res, 0, f64=True)
+        bad, _ = oracle.count_mismatches(32, dres.cpu().numpy(), want)
+        assert bad == 0
+
+
+def test_config4_convolution_shape(cuda):
+    # batch 32, 64 -> 128 channels, 56x56, 3x3, pad 1: checked on 4 of the 32 images against the oracle, then the full
+    # batch against per-image calls
+    torch = cuda
+    rng = np.random.default_rng(3)
+    worst = check_conv(torch, rng, 32, 151, 64, 56, 56, 3, 3, 1, 1, 1, 128, 4, weight_scale=0.05)
+    assert worst < 1e-4
+    g = torch.Generator(device="cuda").manual_seed(0)
+    im = torch.rand(32 * 64 * 56 * 56, generator=g, device="cuda") * 2 - 1
+    w = torch.randn(128 * 64 * 9, generator=g, device="cuda") * 0.05
+    full = torch.full((32 * 128 * 56 * 56,), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    assert cb.Convgemm(151, 64, 56, 56, 3, 3, 1, 1, 1, 1, 1, 1, 128, 32, im, 0, w, 0, full, 0) == 0
+    per = 128 * 56 * 56
+    for n in (0, 13, 31):
+        one = torch.full((per,), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        assert cb.Convgemm(151, 64, 56, 56, 3, 3, 1, 1, 1, 1, 1, 1, 128, 1, im, n * 64 * 56 * 56, w, 0, one, 0) == 0
+        assert torch.equal(one, full[n * per:(n + 1) * per])
