@@ -251,6 +251,14 @@ int run(const GemmDesc& d, void* stream, int async) {
     std::fprintf(stderr, "b200blas: CUDA error %d (%s)\n", static_cast<int>(err), cudaGetErrorString(err));
     return static_cast<int>(err);
   }
+  if (!async && std::strncmp(t_last_kernel, "tc_", 3) == 0) {
+    // The tensor-core kernel reports expired waits through a status word instead of hanging or trapping.
+    unsigned int status[4] = {0, 0, 0, 0};
+    if (tc_f16_status(status, true) == cudaSuccess && status[0] != 0) {
+      std::fprintf(stderr, "b200blas: tensor-core kernel gave up waiting (code %u, block %u)\n", status[0], status[1]);
+      return kUnexpectedError;
+    }
+  }
   return kSuccess;
 }
 
@@ -375,13 +383,14 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
   // kernel's compute type (float for half and single, double, or (re, im) pairs).
   const size_t scalar_bytes = (dtype == 16 || dtype == 32) ? 4 : (dtype == 64 || dtype == 3232) ? 8 : 16;
   const size_t off_bytes = batch_count * sizeof(long long);
+  const size_t off_block = (3 * off_bytes + 15) / 16 * 16;  // keeps the scalar tables 16-byte aligned
   const size_t sc_bytes = (batch_count * scalar_bytes + 15) / 16 * 16;
-  const size_t total = 3 * off_bytes + 2 * sc_bytes;
+  const size_t total = off_block + 2 * sc_bytes;
   std::vector<unsigned char> host(total);
   long long* h_a = reinterpret_cast<long long*>(host.data());
   long long* h_b = h_a + batch_count;
   long long* h_c = h_b + batch_count;
-  unsigned char* h_alpha = host.data() + 3 * off_bytes;
+  unsigned char* h_alpha = host.data() + off_block;
   unsigned char* h_beta = h_alpha + sc_bytes;
   for (size_t i = 0; i < batch_count; ++i) {
     h_a[i] = static_cast<long long>(swapped ? b_offsets[i] : a_offsets[i]);
@@ -423,8 +432,8 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
     d.a_offs = reinterpret_cast<const long long*>(dev);
     d.b_offs = d.a_offs + batch_count;
     d.c_offs = d.b_offs + batch_count;
-    d.alphas = dev + 3 * off_bytes;
-    d.betas = dev + 3 * off_bytes + sc_bytes;
+    d.alphas = dev + off_block;
+    d.betas = dev + off_block + sc_bytes;
     err = dispatch(d, s);
   }
   if (dev) {

@@ -1,4 +1,407 @@
+// HGEMM on the 5th-generation tensor cores: TMA -> shared-memory ring -> tcgen05.mma (kind::f16, fp32 accumulators
+// in TMEM) -> tcgen05.ld epilogue. Persistent, warp-specialised, one CTA per SM.
+//
+// This kernel replaces, for half precision, the reference's "indirect" GEMM path: the Xgemm kernel plus its
+// copy/pad/transpose pre- and post-kernels and the temporary buffers they need
+// (src/routines/level3/xgemm.cpp:101-222, src/kernels/level3/xgemm_part3.opencl:53-305, copy_pad.opencl,
+// transpose_pad.opencl). Edge tiles are zero-filled by the TMA unit and masked in the epilogue, so nothing is
+// padded or transposed in memory. The reference accumulates half GEMMs in half; here products are exact and
+// sums are fp32, rounded to half once (alpha*acc + beta*c is evaluated in fp32).
+//
+// Operand requirements (checked on the host, otherwise the CUDA-core kernel runs): both operands K-contiguous
+// after normalisation, 16-byte aligned base addresses and leading dimensions that are multiples of 8 elements.
+//
+// Roles per CTA (192 threads): warp 0 lane 0 issues TMA loads; warp 1 owns TMEM and lane 0 issues the MMAs;
+// warps 2-5 drain accumulators (each warp reads the 32 TMEM lanes its rank modulo 4 may access).
+// Every wait is bounded: on expiry the CTA records a code in g_tc_status, all roles leave their loops, copies
+// already in flight are waited for (bounded again), TMEM is released and the kernel returns.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../driver_api.h"
 #include "launchers.h"
+
 namespace b200 {
-cudaError_t launch_tc_f16(const GemmDesc&, cudaStream_t, const char**) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int BM = 128;      // MMA M: rows of op(A) per tile (TMEM lanes)
+constexpr int BN = 256;      // MMA N: columns of op(B) per tile (TMEM columns per accumulator)
+constexpr int BK = 64;       // K per stage: 64 halves = one 128-byte swizzle row
+constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit inputs
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;  // two accumulators of BN fp32 columns
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_CYCLES = 4000000000LL;  // about two seconds at 2 GHz
+
+// [0] first timeout code seen (0 = none), [1] block that saw it, [2] role-specific detail.
+__device__ unsigned int g_tc_status[4];
+
+struct TcParams {
+  __half* c;
+  long long ldc;
+  int m, n, k;          // normalised extents: C is m x n with m contiguous
+  int tiles_m, tiles_n;
+  int k_blocks;
+  float alpha, beta;
+  int raster_group;     // m-tiles per rasterisation group
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false when the wait expired or another role already raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - start > WAIT_CYCLES) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_tc_status[0], 0u, code) == 0u) {
+          g_tc_status[1] = blockIdx.x;
+          g_tc_status[2] = bar;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
+// start address / 16 in bits 0-13, leading byte offset (unused for swizzled K-major, set to 1) in bits 16-29,
+// stride byte offset = 1024 bytes (8 rows) / 16 in bits 32-45, descriptor version 1 in bits 46-47, layout type
+// 2 (128-byte swizzle) in bits 61-63.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulator (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15,
+// 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Tiles are walked in groups of `raster_group` m-tiles by all n-tiles, m fastest inside a group, so the CTAs
+// running at the same time share a small set of operand rows in L2.
+__device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm, int& tn) {
+  const int per_group = p.raster_group * p.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * p.raster_group;
+  const int rows = min(p.raster_group, p.tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+  uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES);
+  // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;  // stages armed so far (bounded by STAGES for the teardown wait)
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
+          const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_BYTES;
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, tm * BM);
+          tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, tn * BN);
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Abort path: the copies already issued still land in shared memory; give each armed stage a bounded
+        // chance to complete before the CTA may exit.
+        const int pending = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < pending; ++i) {
+          const long long start = clock64();
+          int s = stage - 1 - i;
+          if (s < 0) s += STAGES;
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+          while (!mbar_try_wait(full_bar(s), par) && clock64() - start < WAIT_CYCLES / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
+          const uint32_t b_src = a_src + A_BYTES;
+          const uint64_t da = kmajor_sw128_desc(a_src);
+          const uint64_t db = kmajor_sw128_desc(b_src);
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            // advancing K by 16 halves = 32 bytes inside the swizzle row = 2 units of the address field
+            umma_f16(d_tmem, da + 2u * ks, db + 2u * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once the MMAs above have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5 ----
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    int local = 0;
+    bool ok = true;
+    const bool use_beta = p.beta != 0.f;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u);
+      ok = __all_sync(0xffffffffu, ok);  // also reconverges the warp before the warp-wide TMEM loads
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = tm * BM + quad * 32 + lane;  // m index of this thread
+      const bool row_ok = row < p.m;
+      const int col0 = tn * BN;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        if (col0 + cb * 32 >= p.n) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32cols(t_row + cb * 32, r);
+        if (row_ok) {
+          __half* cptr = p.c + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + cb * 32 + j < p.n) {
+              float v = p.alpha * __uint_as_float(r[j]);
+              if (use_beta) v += p.beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
+              cptr[static_cast<long long>(j) * p.ldc] = __float2half_rn(v);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
+  const DriverApi& drv = driver_api();
+  if (!drv.ok) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
+                                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t tc_f16_status(unsigned int out[4], bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_status, sizeof(unsigned int) * 4);
+  if (e == cudaSuccess && clear && out[0] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_tc_status, zero, sizeof(zero));
+  }
+  return e;
+}
+
+cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name) {
+  if (d.dtype != 16 || d.is_conv || d.batch != 1 || d.force_small) return cudaErrorNotSupported;
+  if (!d.a_kcontig || !d.b_kcontig) return cudaErrorNotSupported;
+  if (d.m < 128 || d.n < 64 || d.k < 64) return cudaErrorNotSupported;
+  if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
+  const __half* a = static_cast<const __half*>(d.a) + d.a_off;
+  const __half* b = static_cast<const __half*>(d.b) + d.b_off;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
+  if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorNotSupported;
+  // TMA strides must stay below 2^40 bytes
+  if (d.lda * 2 >= (1LL << 40) || d.ldb * 2 >= (1LL << 40)) return cudaErrorNotSupported;
+
+  CUtensorMap map_a, map_b;
+  if (!encode_operand_map(&map_a, a, d.m, d.k, d.lda, BM)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, b, d.n, d.k, d.ldb, BN)) return cudaErrorNotSupported;
+
+  TcParams p;
+  p.c = static_cast<__half*>(d.c) + d.c_off;
+  p.ldc = d.ldc;
+  p.m = static_cast<int>(d.m);
+  p.n = static_cast<int>(d.n);
+  p.k = static_cast<int>(d.k);
+  p.tiles_m = static_cast<int>((d.m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((d.n + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
+  p.alpha = static_cast<float>(d.alpha[0]);
+  p.beta = static_cast<float>(d.beta[0]);
+  p.raster_group = 16;
+
+  // Per-device one-time set-up: SM count and the opt-in to more than 48 KB of dynamic shared memory.
+  static int sm_counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
+  if (sm_counts[dev] == 0) {
+    int count = 0;
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    const cudaError_t e =
+        cudaFuncSetAttribute(hgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    sm_counts[dev] = count;
+  }
+  const int sm_count = sm_counts[dev];
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  *name = "tc_f16_128x256x64";
+  hgemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return cudaGetLastError();
+}
+
+}  // namespace b200
