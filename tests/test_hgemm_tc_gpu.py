@@ -90,7 +90,8 @@ def test_config3_hgemm_8192_sampled(cuda):
         assert cb.Gemm(H.ROW, H.NO, H.YES, m, n, k, 1.0, a, 0, k, b, 0, k, 0.0, c1, 0, n) == 0
         assert cb.last_kernel().startswith("tc_")
         assert cb.Gemm(H.ROW, H.NO, H.YES, m, n, k, 2.0, a, 0, k, b, 0, k, 0.0, c2, 0, n) == 0
-        assert torch.equal(c2, c1 * 2)
+        normal = c1.abs() >= 2.0 ** -13  # doubling is exact except for results in half's subnormal range
+        assert torch.equal(c2[normal], c1[normal] * 2) and int(normal.sum()) > 0.99 * m * n
         rs = np.random.default_rng(m)
         rows, cols = rs.integers(0, m, 4096), rs.integers(0, n, 4096)
         want, mag = oracle.gemm_f64_sampled(16, H.ROW, H.NO, H.YES, k, 1.0, a.cpu().numpy(), 0, k, b.cpu().numpy(), 0, k,
