@@ -3,13 +3,13 @@
 The product is ``lib/libclblast.so`` (hand-written sm_100a CUDA kernels behind a C ABI and the reference's C++
 API symbols); this package is the Python binding used by the tests and the benchmark.
 """
-from .api import (ClearCache, Convgemm, FillCache, Gemm, GemmBatched, GemmStridedBatched, GemmTempBufferSize,
+from .api import (ClearCache, Convgemm, FillCache, Gemm, GemmBatched, GemmBatchedStatic, GemmStridedBatched, GemmTempBufferSize,
                   KernelMode, Layout, OverrideParameters, Precision, RetrieveParameters, StatusCode, Transpose,
                   last_kernel, launch_count)
 from ._lib import LIB_PATH, LibraryMissing, lib
 
 __all__ = [
-    "ClearCache", "Convgemm", "FillCache", "Gemm", "GemmBatched", "GemmStridedBatched", "GemmTempBufferSize",
+    "ClearCache", "Convgemm", "FillCache", "Gemm", "GemmBatched", "GemmBatchedStatic", "GemmStridedBatched", "GemmTempBufferSize",
     "KernelMode", "Layout", "OverrideParameters", "Precision", "RetrieveParameters", "StatusCode", "Transpose",
     "last_kernel", "launch_count", "LIB_PATH", "LibraryMissing", "lib",
 ]

@@ -32,6 +32,8 @@ def lib() -> ctypes.CDLL:
     L.b200blas_gemm_batched.restype = i
     L.b200blas_gemm_batched.argtypes = [i, i, i, i, sz, sz, sz, vp, vp, POINTER(sz), sz, vp, POINTER(sz), sz, vp, vp,
                                         POINTER(sz), sz, sz, vp, i]
+    L.b200blas_gemm_batched_static.restype = i
+    L.b200blas_gemm_batched_static.argtypes = L.b200blas_gemm_batched.argtypes
     L.b200blas_convgemm.restype = i
     L.b200blas_convgemm.argtypes = [i, i] + [sz] * 13 + [vp, sz, vp, sz, vp, sz, vp, i]
     L.b200blas_gemm_temp_buffer_size.restype = i
@@ -56,7 +58,8 @@ def lib() -> ctypes.CDLL:
 
 # Every symbol include/b200blas.h declares; tests check that the built library exports all of them.
 C_ABI_SYMBOLS = [
-    "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_convgemm",
+    "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_gemm_batched_static",
+    "b200blas_convgemm",
     "b200blas_gemm_temp_buffer_size", "b200blas_clear_cache", "b200blas_fill_cache", "b200blas_override_parameters",
     "b200blas_retrieve_parameters", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
 ]

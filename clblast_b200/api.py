@@ -165,6 +165,32 @@ def GemmBatched(layout, a_transpose, b_transpose, m, n, k, alphas: Sequence, a_b
         c_ld, batch_count, sp, is_async))
 
 
+STATIC_MAX_BATCHES = 4096
+
+
+def GemmBatchedStatic(layout, a_transpose, b_transpose, m, n, k, alphas: Sequence, a_buffer, a_offsets: Sequence[int],
+                      a_ld, b_buffer, b_offsets: Sequence[int], b_ld, betas: Sequence, c_buffer,
+                      c_offsets: Sequence[int], c_ld, batch_count, *, stream, wait=True, precision=None):
+    """GemmBatched for callers that cannot allocate device memory (a process whose arena owns the whole GPU, a
+    latency-critical loop): the per-batch tables live in a fixed array inside the library, so at most
+    ``STATIC_MAX_BATCHES`` batches per call, calls on one GPU must not overlap, and the work always runs on the
+    caller's ``stream`` (``wait`` synchronises it). No counterpart in the reference."""
+    p = precision_of(c_buffer, precision)
+    npdt = _NP_OF[p]
+    al = np.ascontiguousarray(np.asarray(alphas, dtype=npdt))
+    be = np.ascontiguousarray(np.asarray(betas, dtype=npdt))
+    if len(al) != batch_count or len(be) != batch_count or len(a_offsets) != batch_count or \
+            len(b_offsets) != batch_count or len(c_offsets) != batch_count:
+        return StatusCode.kInvalidBatchCount
+    arr = ctypes.c_size_t * max(batch_count, 1)
+    ao, bo, co = arr(*a_offsets), arr(*b_offsets), arr(*c_offsets)
+    sp = ctypes.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
+    return _status(lib().b200blas_gemm_batched_static(
+        p, int(layout), int(a_transpose), int(b_transpose), m, n, k, al.ctypes.data_as(ctypes.c_void_p),
+        _ptr(a_buffer), ao, a_ld, _ptr(b_buffer), bo, b_ld, be.ctypes.data_as(ctypes.c_void_p), _ptr(c_buffer), co,
+        c_ld, batch_count, sp, 1 if wait else 0))
+
+
 def Convgemm(kernel_mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dilation_h,
              dilation_w, num_kernels, batch_count, im_buffer, im_offset, kernel_buffer, kernel_offset, result_buffer,
              result_offset, *, precision=None, stream=None):

@@ -21,6 +21,7 @@
 
 #include "driver_api.h"
 #include "kernels/launchers.h"
+#include "noalloc_bridge.h"
 #include "params_store.h"
 
 namespace b200 {
@@ -270,6 +271,93 @@ bool force_small_family(int dtype, size_t m, size_t n, size_t k) {
 }
 
 }  // namespace
+
+// ---- bridge for the allocation-free batched entry point ------------------------------------------------------
+// Same argument checks, normalisation and table layout as b200blas_gemm_batched above, but the tables are written
+// into a caller-provided host block and nothing is enqueued; the caller copies the block to its own device
+// scratch, calls patch_batched_tables() with that address and launches with dispatch_desc().
+int prepare_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k, const void* alphas,
+                    const void* a, const size_t* a_offsets, size_t a_ld, const void* b, const size_t* b_offsets,
+                    size_t b_ld, const void* betas, void* c, const size_t* c_offsets, size_t c_ld, size_t batch_count,
+                    unsigned char* host_block, size_t host_capacity, GemmDesc* out, BatchedTables* tables) {
+  const size_t elem = dtype_size(dtype);
+  if (elem == 0 || !valid_enums(layout, ta, tb)) return kUnexpectedError;
+  if (batch_count < 1 || !alphas || !betas || !a_offsets || !b_offsets || !c_offsets) return kInvalidBatchCount;
+  if (m == 0 || n == 0 || k == 0) return kInvalidDimension;
+  const Extents e = extents(layout, ta, tb, m, n, k);
+  size_t a_max = 0, b_max = 0, c_max = 0;
+  for (size_t i = 0; i < batch_count; ++i) {
+    if (a_offsets[i] > a_max) a_max = a_offsets[i];
+    if (b_offsets[i] > b_max) b_max = b_offsets[i];
+    if (c_offsets[i] > c_max) c_max = c_offsets[i];
+  }
+  int st = test_matrix(e.a_one, e.a_two, a, a_max, a_ld, elem, false, kInvalidLeadDimA, kInsufficientMemoryA,
+                       kInvalidMatrixA);
+  if (st) return st;
+  st = test_matrix(e.b_one, e.b_two, b, b_max, b_ld, elem, false, kInvalidLeadDimB, kInsufficientMemoryB,
+                   kInvalidMatrixB);
+  if (st) return st;
+  st = test_matrix(e.c_one, e.c_two, c, c_max, c_ld, elem, true, kInvalidLeadDimC, kInsufficientMemoryC,
+                   kInvalidMatrixC);
+  if (st) return st;
+
+  GemmDesc d = {};
+  d.dtype = dtype;
+  normalise(d, layout, ta, tb, m, n, k, a, a_ld, b, b_ld, c, c_ld, e);
+  const bool swapped = (layout == kRowMajor);
+  d.batch = static_cast<long long>(batch_count);
+  d.force_small = force_small_family(dtype, m, n, k);
+
+  const size_t scalar_bytes = (dtype == 16 || dtype == 32) ? 4 : (dtype == 64 || dtype == 3232) ? 8 : 16;
+  const size_t off_bytes = batch_count * sizeof(long long);
+  tables->off_block = (3 * off_bytes + 15) / 16 * 16;
+  tables->sc_bytes = (batch_count * scalar_bytes + 15) / 16 * 16;
+  tables->total = tables->off_block + 2 * tables->sc_bytes;
+  tables->batch_count = batch_count;
+  if (tables->total > host_capacity) return kInvalidBatchCount;
+  long long* h_a = reinterpret_cast<long long*>(host_block);
+  long long* h_b = h_a + batch_count;
+  long long* h_c = h_b + batch_count;
+  unsigned char* h_alpha = host_block + tables->off_block;
+  unsigned char* h_beta = h_alpha + tables->sc_bytes;
+  for (size_t i = 0; i < batch_count; ++i) {
+    h_a[i] = static_cast<long long>(swapped ? b_offsets[i] : a_offsets[i]);
+    h_b[i] = static_cast<long long>(swapped ? a_offsets[i] : b_offsets[i]);
+    h_c[i] = static_cast<long long>(c_offsets[i]);
+    double al[2], be[2];
+    read_scalar(dtype, alphas, i, al);
+    read_scalar(dtype, betas, i, be);
+    if (dtype == 16 || dtype == 32) {
+      reinterpret_cast<float*>(h_alpha)[i] = static_cast<float>(al[0]);
+      reinterpret_cast<float*>(h_beta)[i] = static_cast<float>(be[0]);
+    } else if (dtype == 64) {
+      reinterpret_cast<double*>(h_alpha)[i] = al[0];
+      reinterpret_cast<double*>(h_beta)[i] = be[0];
+    } else if (dtype == 3232) {
+      reinterpret_cast<float*>(h_alpha)[2 * i] = static_cast<float>(al[0]);
+      reinterpret_cast<float*>(h_alpha)[2 * i + 1] = static_cast<float>(al[1]);
+      reinterpret_cast<float*>(h_beta)[2 * i] = static_cast<float>(be[0]);
+      reinterpret_cast<float*>(h_beta)[2 * i + 1] = static_cast<float>(be[1]);
+    } else {
+      reinterpret_cast<double*>(h_alpha)[2 * i] = al[0];
+      reinterpret_cast<double*>(h_alpha)[2 * i + 1] = al[1];
+      reinterpret_cast<double*>(h_beta)[2 * i] = be[0];
+      reinterpret_cast<double*>(h_beta)[2 * i + 1] = be[1];
+    }
+  }
+  *out = d;
+  return kSuccess;
+}
+
+void patch_batched_tables(GemmDesc* d, const BatchedTables& t, const unsigned char* device_block) {
+  d->a_offs = reinterpret_cast<const long long*>(device_block);
+  d->b_offs = d->a_offs + t.batch_count;
+  d->c_offs = d->b_offs + t.batch_count;
+  d->alphas = device_block + t.off_block;
+  d->betas = device_block + t.off_block + t.sc_bytes;
+}
+
+cudaError_t dispatch_desc(const GemmDesc& d, cudaStream_t stream) { return dispatch(d, stream); }
 
 }  // namespace b200
 

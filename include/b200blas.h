@@ -46,6 +46,24 @@ int b200blas_gemm_batched(int dtype, int layout, int a_transpose, int b_transpos
                           const size_t* b_offsets, size_t b_ld, const void* betas, void* c, const size_t* c_offsets,
                           size_t c_ld, size_t batch_count, void* stream, int async);
 
+/* GemmBatched without any device allocation. It has no counterpart in the reference, whose GemmBatched allocates
+ * and uploads five device arrays per call (src/routines/levelx/xgemmbatched.cpp:87-90,255-260).
+ * For programs that cannot allocate device memory when they call: processes whose own arena already owns all of
+ * the GPU's memory, and latency-critical loops that must stay clear of the allocator's locks and implicit
+ * synchronisation. The per-batch offset and scalar tables go into a fixed array inside the library image instead
+ * of allocator scratch. Same arguments, checks and results as b200blas_gemm_batched, except:
+ *   - batch_count may not exceed B200BLAS_STATIC_MAX_BATCHES (kInvalidBatchCount, -2049, otherwise);
+ *   - the work is always enqueued on the caller's `stream`; `wait != 0` synchronises that stream before returning;
+ *   - all calls on one GPU share the array (about 224 KB per GPU, held until the process exits) and it keeps the
+ *     last call's tables, so calls that could overlap on the GPU (other streams, other threads) must be ordered
+ *     by the caller;
+ *   - the first call on each device resolves the array's device address; make it before any stream capture. */
+#define B200BLAS_STATIC_MAX_BATCHES 4096
+int b200blas_gemm_batched_static(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n,
+                                 size_t k, const void* alphas, const void* a, const size_t* a_offsets, size_t a_ld,
+                                 const void* b, const size_t* b_offsets, size_t b_ld, const void* betas, void* c,
+                                 const size_t* c_offsets, size_t c_ld, size_t batch_count, void* stream, int wait);
+
 /* Replaces clblast::Convgemm<T> (include/clblast_cuda.h:486-493, src/clblast_cuda.cpp:1625-1645,
  * src/routines/levelx/xconvgemm.cpp:50-161). dtype 16, 32 or 64. */
 int b200blas_convgemm(int dtype, int kernel_mode, size_t channels, size_t height, size_t width, size_t kernel_h,
