@@ -56,8 +56,10 @@ struct TraitsF32 {
   static __device__ __forceinline__ S zero() { return 0.f; }
   static __device__ __forceinline__ S conj(S v) { return v; }
   static __device__ __forceinline__ void mad(S& c, S a, S b) { c = fmaf(a, b, c); }
-  static __device__ __forceinline__ S mul(S a, S b) { return a * b; }
-  static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return al * x + be * y; }
+  static __device__ __forceinline__ S mul(S a, S b) { return __fmul_rn(a, b); }
+  // alpha*x + beta*y as fma(beta, y, alpha*x): the fused form of the reference's AXPBY, bit-identical to the
+  // reference kernels compiled with contraction (and to the CPU oracle).
+  static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return fmaf(be, y, __fmul_rn(al, x)); }
   static __device__ __forceinline__ bool is_zero(S v) { return v == 0.f; }
   static __host__ S from_host(const double* v) { return static_cast<float>(v[0]); }
 };
@@ -72,8 +74,8 @@ struct TraitsF64 {
   static __device__ __forceinline__ S zero() { return 0.0; }
   static __device__ __forceinline__ S conj(S v) { return v; }
   static __device__ __forceinline__ void mad(S& c, S a, S b) { c = fma(a, b, c); }
-  static __device__ __forceinline__ S mul(S a, S b) { return a * b; }
-  static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return al * x + be * y; }
+  static __device__ __forceinline__ S mul(S a, S b) { return __dmul_rn(a, b); }
+  static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return fma(be, y, __dmul_rn(al, x)); }
   static __device__ __forceinline__ bool is_zero(S v) { return v == 0.0; }
   static __host__ S from_host(const double* v) { return v[0]; }
 };

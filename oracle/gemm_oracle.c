@@ -7,7 +7,7 @@
  * Parity pin: the reference ships no golden vectors or known-answer files for this path; its tests compare
  * two implementations on seeded random data. This oracle is pinned instead (a) against the reference's own
  * kernel source, compiled for the CPU by oracle/build_ref.py into oracle/_ref/ and executed work-group by
- * work-group (tests/test_oracle.py), and (b) against fixtures under tests/golden/ generated with numpy's
+ * work-group (tests/test_oracle_ref.py: bit-identical for half, single and double), and (b) against fixtures under tests/golden/ generated with numpy's
  * fp64 product.
  *
  * Two flavours of every routine:
@@ -167,7 +167,7 @@ int oracle_gemm_f64_sampled(int dtype, int layout, int ta, int tb, size_t k, dou
 
 /* ---- reference-order, type-T ------------------------------------------------------------------------- */
 
-#define DEFINE_REAL_GEMM(NAME, T, FMA)                                                                         \
+#define DEFINE_REAL_GEMM(NAME, T, FMA, AXPBY)                                                                         \
   static int NAME(int layout, int ta, int tb, size_t m, size_t n, size_t k, T alpha, const T* a, size_t a_off, \
                   size_t a_ld, const T* b, size_t b_off, size_t b_ld, T beta, T* c, size_t c_off, size_t c_ld) { \
     T* ap = (T*)malloc(sizeof(T) * m * k);                                                                     \
@@ -188,7 +188,10 @@ int oracle_gemm_f64_sampled(int dtype, int layout, int ta, int tb, size_t k, dou
         }                                                                                                      \
         for (size_t j = 0; j < n; ++j) {                                                                       \
           const size_t ci = c_off + ((layout == ROW_MAJOR) ? i * c_ld + j : j * c_ld + i);                     \
-          c[ci] = (beta == (T)0) ? (T)(alpha * acc[j]) : (T)(alpha * acc[j] + beta * c[ci]);                   \
+          /* alpha*acc + beta*c evaluated as fma(beta, c, alpha*acc): the contraction the reference's AXPBY     \
+           * (src/kernels/common.opencl:240-244) gets from a fusing compiler; bit-identical to the reference's  \
+           * kernel source executed on the CPU (tests/test_oracle_ref.py). */                                  \
+          c[ci] = (beta == (T)0) ? (T)(alpha * acc[j]) : (T)(AXPBY(alpha, acc[j], beta, c[ci]));                            \
         }                                                                                                      \
       }                                                                                                        \
       free(acc);                                                                                               \
@@ -199,12 +202,18 @@ int oracle_gemm_f64_sampled(int dtype, int layout, int ta, int tb, size_t k, dou
 
 #define FMA_F32(a, b, c) fmaf((a), (b), (c))
 #define FMA_F64(a, b, c) fma((a), (b), (c))
-/* Half: product and sum each rounded to half, the unfused form of the reference's `acc += a*b` in half. */
-#define FMA_F16(a, b, c) ((f16)((f16)((a) * (b)) + (c)))
+/* Half: the product of two halves is exact in float; the sum is formed in float and rounded to half, which is
+ * what `acc += a*b` on half operands gives on a target that evaluates half arithmetic in float. */
+#define FMA_F16(a, b, c) ((f16)((float)(a) * (float)(b) + (float)(c)))
 
-DEFINE_REAL_GEMM(gemm_f32, float, FMA_F32)
-DEFINE_REAL_GEMM(gemm_f64, double, FMA_F64)
-DEFINE_REAL_GEMM(gemm_f16, f16, FMA_F16)
+#define AXPBY_F32(al, x, be, y) fmaf((be), (y), (al) * (x))
+#define AXPBY_F64(al, x, be, y) fma((be), (y), (al) * (x))
+/* Half: both products are exact in float, one float addition, one rounding to half. */
+#define AXPBY_F16(al, x, be, y) ((f16)((float)(al) * (float)(x) + (float)(be) * (float)(y)))
+
+DEFINE_REAL_GEMM(gemm_f32, float, FMA_F32, AXPBY_F32)
+DEFINE_REAL_GEMM(gemm_f64, double, FMA_F64, AXPBY_F64)
+DEFINE_REAL_GEMM(gemm_f16, f16, FMA_F16, AXPBY_F16)
 
 #define DEFINE_COMPLEX_GEMM(NAME, R)                                                                           \
   static int NAME(int layout, int ta, int tb, size_t m, size_t n, size_t k, const R* alpha, const R* a,        \
@@ -280,9 +289,13 @@ void oracle_conv_output_size(size_t height, size_t width, size_t kernel_h, size_
   *out_w = (size_w >= padding_w) ? (size_w - padding_w) / stride_w + 1 : 1;
 }
 
-/* Seven nested loops in the order of the reference's own host check (test/routines/levelx/xconvgemm.hpp:151-196):
- * channels, then kernel rows, then kernel columns; kConvolution mirrors the weight index. `result64` (double) is
- * written when non-null, else `result` in the dtype with accumulation in the dtype. Real dtypes only. */
+/* Direct convolution with the summation order of the reference KERNEL (src/kernels/levelx/xconvgemm_part1.opencl:
+ * 31-53, xconvgemm_part2.opencl:27-285): for each output pixel and output channel, k = (channel, kh, kw) runs
+ * ascending over the WEIGHT index and the image tap is taken at (kh, kw), mirrored to (KH-1-kh, KW-1-kw) for
+ * kConvolution; taps outside the image contribute zero. (The reference's host-side test loop,
+ * test/routines/levelx/xconvgemm.hpp:151-196, forms the same sum with the weight index mirrored instead.)
+ * `result64` (double) is written when non-null, else `result` in the dtype with accumulation in the dtype.
+ * Real dtypes only. */
 int oracle_convgemm(int dtype, int mode, size_t channels, size_t height, size_t width, size_t kernel_h, size_t kernel_w,
                     size_t pad_h, size_t pad_w, size_t stride_h, size_t stride_w, size_t dil_h, size_t dil_w,
                     size_t num_kernels, size_t batch_count, const void* im, size_t im_off, const void* ker,
@@ -302,13 +315,13 @@ int oracle_convgemm(int dtype, int mode, size_t channels, size_t height, size_t 
           for (size_t ci = 0; ci < channels; ++ci) {
             for (size_t kh = 0; kh < kernel_h; ++kh) {
               for (size_t kw = 0; kw < kernel_w; ++kw) {
-                const long long hi = (long long)(kh * dil_h + stride_h * ho) - (long long)pad_h;
-                const long long wi = (long long)(kw * dil_w + stride_w * wo) - (long long)pad_w;
+                const size_t th = (mode == MODE_CONVOLUTION) ? kernel_h - kh - 1 : kh;
+                const size_t tw = (mode == MODE_CONVOLUTION) ? kernel_w - kw - 1 : kw;
+                const long long hi = (long long)(th * dil_h + stride_h * ho) - (long long)pad_h;
+                const long long wi = (long long)(tw * dil_w + stride_w * wo) - (long long)pad_w;
                 if (hi < 0 || hi >= (long long)height || wi < 0 || wi >= (long long)width) continue;
                 const size_t ii = (size_t)wi + width * ((size_t)hi + height * (ci + channels * nb)) + im_off;
-                const size_t ki = (mode == MODE_CONVOLUTION)
-                                      ? (kernel_w - kw - 1) + kernel_w * ((kernel_h - kh - 1) + kernel_h * (ci + channels * co))
-                                      : kw + kernel_w * (kh + kernel_h * (ci + channels * co));
+                const size_t ki = kw + kernel_w * (kh + kernel_h * (ci + channels * co));
                 double x, y, u;
                 load2(dtype, im, ii, &x, &u);
                 load2(dtype, ker, ki + ker_off, &y, &u);
@@ -317,7 +330,7 @@ int oracle_convgemm(int dtype, int mode, size_t channels, size_t height, size_t 
                 } else if (dtype == 32) {
                   acc32 = fmaf((float)x, (float)y, acc32);
                 } else {
-                  acc16 = (f16)((f16)((f16)x * (f16)y) + acc16);
+                  acc16 = FMA_F16((f16)x, (f16)y, acc16);
                 }
               }
             }

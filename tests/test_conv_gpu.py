@@ -33,6 +33,12 @@ def check_conv(torch, rng, precision, mode, channels, height, width, kh, kw, pad
     mask = np.zeros(res.size, dtype=bool)
     mask[offs[2]:offs[2] + batch * num_kernels * oh * ow] = True
     H.check_against_oracle(precision, got, want, mask, res_in)
+    if precision in (32, 64):
+        # k runs ascending over (channel, kh, kw) with fused multiply-adds, as in the reference kernel: bit-identical
+        typed = np.zeros_like(res)
+        oracle.convgemm(precision, mode, channels, height, width, kh, kw, pad, pad, stride, stride, dil, dil,
+                        num_kernels, batch, im, offs[0], ker, offs[1], typed, offs[2])
+        assert np.array_equal(got[mask].view(np.uint8), typed[mask].view(np.uint8)), "not bit-identical to the oracle"
     return np.abs(got[mask].astype(np.float64) - want[mask]).max()
 
 

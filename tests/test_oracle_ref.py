@@ -1,0 +1,87 @@
+"""Pins the C oracle to the reference's own kernel source.
+
+oracle/_ref/libclblast_ref_kernels.so is the reference's XgemmDirect{NN,NT,TN,TT} and XconvgemmNormal/Flip OpenCL-C
+kernels compiled for the CPU and executed work-group by work-group (oracle/build_ref.py). On the reference's test
+grid (sizes {7, 64}, both layouts, all transposes, offsets, alpha/beta) the oracle's reference-order flavour must
+reproduce those kernels bit for bit for half, single and double, and to rounding level for the complex types (whose
+multiply-add the C compiler is free to fuse in several ways)."""
+import itertools
+
+import numpy as np
+import pytest
+
+from oracle import cpu_oracle as oracle
+from oracle import ref_kernels as ref
+
+pytestmark = pytest.mark.skipif(not ref.available(), reason="reference tree and prebuilt oracle/_ref both absent")
+
+
+def rand(rng, precision, size, lo=-2.0, hi=2.0):
+    x = rng.uniform(lo, hi, size)
+    if precision > 100:
+        x = x + 1j * rng.uniform(lo, hi, size)
+    return x.astype(oracle.NP_OF[precision])
+
+
+@pytest.mark.parametrize("precision", (16, 32, 64, 3232, 6464))
+def test_gemm_oracle_reproduces_the_reference_direct_kernels(precision):
+    rng = np.random.default_rng(42)
+    trs = (111, 112, 113) if precision > 100 else (111, 112)
+    cases = 0
+    for layout, ta, tb in itertools.product((101, 102), trs, trs):
+        for (m, n, k), off in zip(((7, 64, 7), (64, 7, 64), (64, 64, 64), (7, 7, 7), (13, 21, 9)), (0, 10, 0, 10, 3)):
+            ar, ac = (m, k) if ta == 111 else (k, m)
+            br, bc = (k, n) if tb == 111 else (n, k)
+            a_ld = (ac if layout == 101 else ar) + off % 4
+            b_ld = (bc if layout == 101 else br) + off % 3
+            c_ld = (n if layout == 101 else m) + off % 5
+            a = rand(rng, precision, off + a_ld * (ar if layout == 101 else ac))
+            b = rand(rng, precision, off + b_ld * (br if layout == 101 else bc))
+            c = rand(rng, precision, off + c_ld * (m if layout == 101 else n))
+            for alpha, beta in ((3.14, 3.14), (1.0, 0.0), (0.0, 1.0)):
+                if precision > 100:
+                    alpha, beta = alpha + 0.5j, beta - 0.25j if beta else 0.0
+                mine, theirs = c.copy(), c.copy()
+                oracle.gemm(precision, layout, ta, tb, m, n, k, alpha, a, off, a_ld, b, off, b_ld, beta, mine, off, c_ld)
+                ref.gemm_direct(precision, layout, ta, tb, m, n, k, alpha, a, off, a_ld, b, off, b_ld, beta, theirs,
+                                off, c_ld)
+                if precision < 100:
+                    assert np.array_equal(mine.view(np.uint8), theirs.view(np.uint8)), (layout, ta, tb, m, n, k)
+                else:
+                    eps = 2.0 ** -23 if precision == 3232 else 2.0 ** -52
+                    scale = 8.0 * k * abs(alpha) + 2.0 * abs(beta) + 1.0
+                    assert np.abs(mine - theirs).max() <= 4 * eps * scale, (layout, ta, tb, m, n, k)
+                cases += 1
+    assert cases >= 60
+
+
+@pytest.mark.parametrize("precision", (16, 32, 64))
+def test_conv_oracle_reproduces_the_reference_conv_kernels(precision):
+    rng = np.random.default_rng(7)
+    i = 0
+    for mode, pad, dil, ksz, nk, stride, ch in itertools.product((151, 152), (0, 1), (1, 2), (1, 3), (1, 6), (1, 3),
+                                                                 (1, 2)):
+        hw, batch = ((7, 1), (8, 3), (13, 2))[i % 3]
+        off = (0, 10)[i % 2]
+        i += 1
+        oh, ow = oracle.conv_output_size(hw, hw + 1, ksz, ksz, pad, pad, stride, stride, dil, dil)
+        im = rand(rng, precision, off + batch * ch * hw * (hw + 1), -1, 1)
+        ker = rand(rng, precision, off + nk * ch * ksz * ksz, -1, 1)
+        mine = np.zeros(off + batch * nk * oh * ow, dtype=oracle.NP_OF[precision])
+        theirs = mine.copy()
+        oracle.convgemm(precision, mode, ch, hw, hw + 1, ksz, ksz, pad, pad, stride, stride, dil, dil, nk, batch, im, off,
+                        ker, off, mine, off)
+        ref.convgemm(precision, mode, ch, hw, hw + 1, ksz, ksz, pad, pad, stride, stride, dil, dil, nk, batch, im, off, ker,
+                     off, theirs, off)
+        assert np.array_equal(mine.view(np.uint8), theirs.view(np.uint8)), (mode, pad, dil, ksz, nk, stride, ch)
+    assert i == 128
+
+
+def test_conv_kernel_larger_than_image():
+    rng = np.random.default_rng(3)
+    im, ker = rand(rng, 32, 2 * 2 * 2 * 2, -1, 1), rand(rng, 32, 3 * 2 * 9, -1, 1)
+    assert oracle.conv_output_size(2, 2, 3, 3, 0, 0, 1, 1, 2, 2) == (1, 1)
+    mine, theirs = np.zeros(2 * 3, dtype=np.float32), np.zeros(2 * 3, dtype=np.float32)
+    oracle.convgemm(32, 151, 2, 2, 2, 3, 3, 0, 0, 1, 1, 2, 2, 3, 2, im, 0, ker, 0, mine, 0)
+    ref.convgemm(32, 151, 2, 2, 2, 3, 3, 0, 0, 1, 1, 2, 2, 3, 2, im, 0, ker, 0, theirs, 0)
+    assert np.array_equal(mine, theirs)
