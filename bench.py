@@ -49,6 +49,14 @@ WORKLOADS = {
                          beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
     "dgemm_8192": dict(kind="gemm", precision=64, layout=COL, ta=NO, tb=NO, m=8192, n=8192, k=8192, alpha=1.0,
                        beta=0.0, dist="uniform1", bound="fp64"),
+    # Config 5: one large column-major GEMM sharded by column blocks of C over the ranks (strong scaling); A is
+    # broadcast from rank 0 in every step, B and C blocks are resident on their ranks.
+    "dgemm_32768_sharded": dict(kind="sharded", precision=64, layout=COL, ta=NO, tb=NO, m=32768, n=32768, k=32768,
+                                alpha=1.0, beta=0.0, dist="uniform1", bound="fp64"),
+    "sgemm_65536_sharded": dict(kind="sharded", precision=32, layout=COL, ta=NO, tb=NO, m=65536, n=65536, k=65536,
+                                alpha=1.0, beta=0.0, dist="uniform1", bound="fp32"),
+    "sgemm_16384_sharded": dict(kind="sharded", precision=32, layout=COL, ta=NO, tb=NO, m=16384, n=16384, k=16384,
+                                alpha=1.0, beta=0.0, dist="uniform1", bound="fp32"),
     "batched_32": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=32, n=32, k=32, batch=8192,
                        alpha=1.0, beta=1.0, dist="uniform1", bound="hbm"),
     "batched_64x128x96": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=64, n=128, k=96, batch=2048,
@@ -61,7 +69,7 @@ ELEM = {16: 2, 32: 4, 64: 8}
 
 
 def flops_of(w, scale_m=1):
-    if w["kind"] == "gemm":
+    if w["kind"] in ("gemm", "sharded"):
         return 2.0 * w["m"] * scale_m * w["n"] * w["k"]
     if w["kind"] == "strided":
         return 2.0 * w["m"] * w["n"] * w["k"] * w["batch"] * scale_m
@@ -73,7 +81,7 @@ def flops_of(w, scale_m=1):
 def min_bytes_of(w):
     """Algorithmic bytes of one launch: every operand read once, C written once (and read once when beta != 0)."""
     e = ELEM[w["precision"]]
-    if w["kind"] == "gemm":
+    if w["kind"] in ("gemm", "sharded"):
         m, n, k = w["m"], w["n"], w["k"]
         return e * (m * k + k * n + m * n * (2 if w["beta"] != 0 else 1))
     if w["kind"] == "strided":
@@ -161,6 +169,26 @@ def make_inputs(torch, w, device, seed, rows_scale=1):
         b = fill(geo["b_ld"] * b_two)
         c = fill(geo["c_ld"] * c_two) if w["beta"] != 0 else torch.full((geo["c_ld"] * c_two,), float("nan"), device=device, dtype=dt)
         return dict(a=a, b=b, c=c, **geo)
+    if w["kind"] == "sharded":
+        from clblast_b200.multi_gpu import split_range
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        m, n, k = w["m"], w["n"], w["k"]
+        j0, j1 = split_range(n, world, 256)[rank]
+        n_local = j1 - j0
+
+        def fill_big(count):  # generated in slices: torch.rand materialises fp32 temporaries
+            out = torch.empty(count, device=device, dtype=dt)
+            step_ = 1 << 28
+            for s0 in range(0, count, step_):
+                e0 = min(count, s0 + step_)
+                out[s0:e0] = (torch.rand(e0 - s0, generator=g, device=device, dtype=torch.float32) * 2 - 1).to(dt)
+            return out
+
+        a = fill_big(m * k)
+        b = fill_big(k * n_local)
+        c = torch.full((m * n_local,), float("nan"), device=device, dtype=dt)
+        return dict(a=a, b=b, c=c, a_ld=m, b_ld=k, c_ld=m, n_local=n_local, j0=j0)
     if w["kind"] == "strided":
         m, n, k, bt = w["m"], w["n"], w["k"], w["batch"] * rows_scale
         return dict(a=fill(bt * m * k), b=fill(bt * k * n), c=fill(bt * m * n), batch=bt)
@@ -179,6 +207,11 @@ def launch(cb, w, t, stream, m_override=None):
         m = m_override or w["m"]
         return cb.Gemm(w["layout"], w["ta"], w["tb"], m, w["n"], w["k"], w["alpha"], t["a"], 0, t["a_ld"], t["b"], 0,
                        t["b_ld"], w["beta"], t["c"], 0, t["c_ld"], stream=stream)
+    if w["kind"] == "sharded":
+        if t["n_local"] == 0:
+            return 0
+        return cb.Gemm(w["layout"], w["ta"], w["tb"], w["m"], t["n_local"], w["k"], w["alpha"], t["a"], 0, t["a_ld"],
+                       t["b"], 0, t["b_ld"], w["beta"], t["c"], 0, t["c_ld"], stream=stream)
     if w["kind"] == "strided":
         m, n, k = w["m"], w["n"], w["k"]
         return cb.GemmStridedBatched(w["layout"], w["ta"], w["tb"], m, n, k, w["alpha"], t["a"], 0, m, m * k, t["b"], 0,
@@ -326,9 +359,23 @@ def main():
     t = make_inputs(torch, w, device, seed=1234 + rank)
     stream = torch.cuda.current_stream()
 
+    # With N > 1 the operand every rank needs whole (B here) is re-broadcast from rank 0 in every step. The broadcast
+    # for step i+1 runs on NCCL's stream into a second buffer while the GEMM of step i runs, so a step costs
+    # max(broadcast, GEMM) in steady state; every step still contains one broadcast and one GEMM.
+    bcast = {"bufs": None, "cur": 0, "work": None}
+    if dist is not None and w["kind"] == "gemm":
+        bcast["bufs"] = [t["b"], torch.empty_like(t["b"])]
+        dist.broadcast(bcast["bufs"][0], src=0)
+        if rank == 0:
+            bcast["bufs"][1].copy_(bcast["bufs"][0])
+
     def step():
-        if dist is not None and w["kind"] == "gemm":
-            dist.broadcast(t["b"], src=0)
+        if bcast["bufs"] is not None:
+            if bcast["work"] is not None:
+                bcast["work"].wait()          # this step's B has arrived (stream-level wait, no host block)
+                bcast["cur"] ^= 1
+            t["b"] = bcast["bufs"][bcast["cur"]]
+            bcast["work"] = dist.broadcast(bcast["bufs"][bcast["cur"] ^ 1], src=0, async_op=True)
         st = launch(cb, w, t, stream)
         if st != 0:
             raise RuntimeError(f"library call failed with status {st}")
@@ -346,6 +393,10 @@ def main():
     ms = time_steps(torch, step, args.steps, 0, dist)
     launches = cb.launch_count() - launches_before
     clocks = sampler.stop()
+    if bcast["work"] is not None:
+        bcast["work"].wait()
+        torch.cuda.synchronize()
+        t["b"] = bcast["bufs"][0]
 
     total_flops = flops_of(w) * n_gpus
     ms_per_step = ms / args.steps
@@ -434,7 +485,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": {16: "f16", 32: "f32", 64: "f64"}[w["precision"]], "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in w.items() if k not in ("kind", "bound")},
-                   "per_gpu": "one full copy of the workload per GPU; B broadcast from rank 0 every step" if n_gpus > 1
+                   "per_gpu": "one full copy of the workload per GPU; B re-broadcast from rank 0 every step, overlapped with the previous step's GEMM" if n_gpus > 1
                    else "single GPU", "l2": "inputs larger than L2 (no flush needed)" if min_bytes_of(w) > 126e6
                    else "working set fits in L2; no flush between iterations"},
         "roofline": roof,
@@ -453,8 +504,8 @@ def main():
     if rank == 0 and n_gpus == 1 and not args.no_sweep:
         sweep = {}
         for name, ww in WORKLOADS.items():
-            if name == args.workload:
-                continue
+            if name == args.workload or ww["kind"] == "sharded":
+                continue  # the sharded config-5 shapes take seconds per launch: run them with --workload
             try:
                 tt = make_inputs(torch, ww, device, seed=99)
                 fn = lambda: launch(cb, ww, tt, stream)

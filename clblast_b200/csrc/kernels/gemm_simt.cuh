@@ -276,11 +276,15 @@ struct TileStager {
 
 // ---- the kernel -----------------------------------------------------------------------------------------
 
-template <typename Tr, int BM, int BN, int BK, int TM, int TN, bool A_KC, bool B_KC, bool CONV, int MINB>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB) gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
+// GROUPS > 1 lets one CTA work on several tiles at once, each tile owned by a group of (BM/TM)*(BN/TN) threads:
+// small batched problems then get a large register tile per thread (high FMA-to-load ratio) and a CTA that is
+// still big enough to keep many loads in flight.
+template <typename Tr, int BM, int BN, int BK, int TM, int TN, bool A_KC, bool B_KC, bool CONV, int MINB, int GROUPS>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, MINB)
+gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
   using T = typename Tr::T;
   using S = typename Tr::S;
-  constexpr int NT = (BM / TM) * (BN / TN);
+  constexpr int NT = (BM / TM) * (BN / TN);  // threads per tile
   constexpr int CW = Tr::CW;
   constexpr int CWM = (TM < CW) ? TM : CW;  // width of one contiguous chunk of rows owned by a thread
   constexpr int CWN = (TN < CW) ? TN : CW;
@@ -292,22 +296,30 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB) gemm_simt_kernel(
   using StA = TileStager<Tr, BM, BK, NT, A_KC>;
   using StB = TileStager<Tr, BN, BK, NT, B_KC>;
 
-  __shared__ __align__(16) S sA[2][BK * LDA_S];
-  __shared__ __align__(16) S sB[2][BK * LDB_S];
+  __shared__ __align__(16) S sA_all[GROUPS][2][BK * LDA_S];
+  __shared__ __align__(16) S sB_all[GROUPS][2][BK * LDB_S];
 
-  const int tid = threadIdx.x;
+  const int group = (GROUPS > 1) ? threadIdx.x / NT : 0;
+  const int tid = (GROUPS > 1) ? threadIdx.x % NT : threadIdx.x;
+  S(*sA)[BK * LDA_S] = sA_all[group];
+  S(*sB)[BK * LDB_S] = sB_all[group];
   const int tx = tid % (BM / TM);
   const int ty = tid / (BM / TM);
   const bool a_vec_ok = (p.lda % Tr::VEC) == 0;
   const bool b_vec_ok = (p.ldb % Tr::VEC) == 0;
 
-  for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+  for (long long first = static_cast<long long>(blockIdx.x) * GROUPS; first < p.total_tiles;
+       first += static_cast<long long>(gridDim.x) * GROUPS) {
+    // A group without a tile in the last round keeps walking through the barriers on a clamped tile and only
+    // skips the stores.
+    const bool active = first + group < p.total_tiles;
+    const long long tile = active ? first + group : p.total_tiles - 1;
     const long long tm = tile % p.tiles_m;
     const long long rest = tile / p.tiles_m;
     const long long tn = rest % p.tiles_n;
     const long long bz = rest / p.tiles_n;
     const long long m0 = tm * BM, n0 = tn * BN;
-    const long long m_rem = p.m - m0, n_rem = p.n - n0;
+    const long long m_rem = p.m - m0, n_rem = active ? p.n - n0 : 0;  // n_rem == 0 masks every store
 
     const T* a_base = static_cast<const T*>(p.a) + (p.a_offs ? p.a_offs[bz] : p.a_off + bz * p.a_stride);
     const T* b_base = static_cast<const T*>(p.b) + (p.b_offs ? p.b_offs[bz] : p.b_off + bz * p.b_stride);
@@ -330,7 +342,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB) gemm_simt_kernel(
       } else {
         StA::fetch(ra, a_base, p.lda, m0, k0, m_rem, p.k - k0, a_vec_ok, tid);
       }
-      StB::fetch(rb, b_base, p.ldb, n0, k0, n_rem, p.k - k0, b_vec_ok, tid);
+      StB::fetch(rb, b_base, p.ldb, n0, k0, p.n - n0, p.k - k0, b_vec_ok, tid);
     };
 
     fetch_tiles(0);
@@ -420,7 +432,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB) gemm_simt_kernel(
 
 // ---- host-side launch -----------------------------------------------------------------------------------
 
-template <typename Tr, int BM, int BN, int BK, int TM, int TN, int MINB>
+template <typename Tr, int BM, int BN, int BK, int TM, int TN, int MINB, int GROUPS = 1>
 struct SimtLauncher {
   using S = typename Tr::S;
 
@@ -444,9 +456,10 @@ struct SimtLauncher {
     p.conj_a = d.conj_a; p.conj_b = d.conj_b;
     p.conv = d.conv;
     const long long max_grid = 1LL << 30;
-    const unsigned grid = static_cast<unsigned>(p.total_tiles < max_grid ? p.total_tiles : max_grid);
-    constexpr int NT = (BM / TM) * (BN / TN);
-    gemm_simt_kernel<Tr, BM, BN, BK, TM, TN, A_KC, B_KC, CONV, MINB><<<grid, NT, 0, stream>>>(p);
+    const long long ctas = (p.total_tiles + GROUPS - 1) / GROUPS;
+    const unsigned grid = static_cast<unsigned>(ctas < max_grid ? ctas : max_grid);
+    constexpr int NT = (BM / TM) * (BN / TN) * GROUPS;
+    gemm_simt_kernel<Tr, BM, BN, BK, TM, TN, A_KC, B_KC, CONV, MINB, GROUPS><<<grid, NT, 0, stream>>>(p);
     return cudaGetLastError();
   }
 

@@ -5,15 +5,13 @@
 namespace b200 {
 
 cudaError_t launch_simt_c64(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  using Large = SimtLauncher<TraitsC64, 64, 64, 8, 4, 4, 1>;
-  using Medium = SimtLauncher<TraitsC64, 64, 64, 8, 4, 4, 1>;
-  using Small = SimtLauncher<TraitsC64, 32, 32, 8, 4, 4, 2>;
-  const SimtClass cls = classify_simt(d);
-
-  switch (cls) {
-    case SimtClass::kLarge: *name = "simt_c64_large"; return Large::launch(d, stream);
-    case SimtClass::kMedium: *name = "simt_c64_medium"; return Medium::launch(d, stream);
-    default: *name = "simt_c64_small"; return Small::launch(d, stream);
+  static const SimtConfig table[] = {
+      {64, 64, 1.0, 1, false},
+      {32, 32, 0.6, 1, true},
+  };
+  switch (pick_simt(d, table, 2)) {
+    case 0: *name = "simt_c64_64x64"; return SimtLauncher<TraitsC64, 64, 64, 8, 4, 4, 1, 1>::launch(d, stream);
+    default: *name = "simt_c64_32x32"; return SimtLauncher<TraitsC64, 32, 32, 8, 4, 4, 2, 1>::launch(d, stream);
   }
 }
 

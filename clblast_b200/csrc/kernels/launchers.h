@@ -23,15 +23,41 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
 // expired in some CTA (1 producer, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready), out[1] is the block.
 cudaError_t tc_f16_status(unsigned int out[4], bool clear);
 
-// Shape classes of the CUDA-core family. kLarge needs enough 128x128 tiles to fill the 148 SMs.
-enum class SimtClass { kSmall, kMedium, kLarge };
+// One tile configuration of the CUDA-core family as seen by the selection table.
+struct SimtConfig {
+  int bm, bn;      // tile extents
+  double eff;      // relative arithmetic efficiency of the configuration on full tiles (1.0 = the 128x128 tile)
+  int groups;      // tiles per CTA
+  bool smallest;   // the configuration forced by GemmRoutine/XGEMM_MIN_INDIRECT_SIZE
+};
 
-inline SimtClass classify_simt(const GemmDesc& d) {
-  const long long mn_min = d.m < d.n ? d.m : d.n;
-  if (d.force_small || mn_min <= 32) return SimtClass::kSmall;
-  const long long tiles_l = ((d.m + 127) / 128) * ((d.n + 127) / 128) * d.batch;
-  if (mn_min >= 96 && tiles_l >= 120) return SimtClass::kLarge;
-  return SimtClass::kMedium;
+// Static selection: the configuration with the best (efficiency x useful fraction of the padded tiles x SM fill).
+inline int pick_simt(const GemmDesc& d, const SimtConfig* cfgs, int count) {
+  double ctas[8], quality[8];
+  double most_ctas = 0.0;
+  if (count > 8) count = 8;
+  for (int i = 0; i < count; ++i) {
+    if (d.force_small && cfgs[i].smallest) return i;
+    const double tiles = static_cast<double>((d.m + cfgs[i].bm - 1) / cfgs[i].bm) *
+                         static_cast<double>((d.n + cfgs[i].bn - 1) / cfgs[i].bn) * static_cast<double>(d.batch);
+    const double useful = (static_cast<double>(d.m) * d.n * d.batch) / (tiles * cfgs[i].bm * cfgs[i].bn);
+    quality[i] = cfgs[i].eff * useful;
+    ctas[i] = tiles / cfgs[i].groups;
+    if (ctas[i] > most_ctas) most_ctas = ctas[i];
+  }
+  // A problem too small to fill the 148 SMs with any configuration is latency-bound: only padding matters then.
+  const bool tiny = most_ctas < 148.0;
+  int best = 0;
+  double best_score = -1.0;
+  for (int i = 0; i < count; ++i) {
+    const double fill = (tiny || ctas[i] >= 148.0) ? 1.0 : ctas[i] / 148.0;
+    const double score = quality[i] * fill;
+    if (score > best_score) {
+      best_score = score;
+      best = i;
+    }
+  }
+  return best;
 }
 
 }  // namespace b200

@@ -26,7 +26,7 @@ def transposes(precision):
 
 
 def run_and_check(torch, rng, precision, layout, ta, tb, m, n, k, alpha, beta, a_off=0, b_off=0, c_off=0,
-                  ld_pad=(0, 0, 0), poison_c=False, expect_kernel=None):
+                  ld_pad=(0, 0, 0), poison_c=False, expect_kernel=None, reject_kernel=None):
     case = H.gemm_case(rng, precision, layout, ta, tb, m, n, k, a_off, b_off, c_off, ld_pad, poison_c=poison_c)
     da, db, dc = (H.to_device(torch, precision, case[x]) for x in "abc")
     torch.cuda.synchronize()
@@ -35,6 +35,8 @@ def run_and_check(torch, rng, precision, layout, ta, tb, m, n, k, alpha, beta, a
     assert st == cb.StatusCode.kSuccess, st
     if expect_kernel:
         assert expect_kernel in cb.last_kernel(), cb.last_kernel()
+    if reject_kernel:
+        assert reject_kernel not in cb.last_kernel(), cb.last_kernel()
     got = H.to_host(precision, dc)
     c_in = case["c"].copy()
     if poison_c:
@@ -76,15 +78,15 @@ def test_reference_grid(cuda, precision):
 def test_ragged_shapes_hit_every_tile_class(cuda, precision):
     rng = np.random.default_rng(7)
     shapes = [(1, 1, 1), (1, 300, 17), (300, 1, 17), (17, 31, 129), (65, 127, 33), (130, 257, 70), (200, 96, 300),
-              (1500, 1300, 70), (1409, 1537, 33)]
+              (1500, 1300, 70), (1409, 1537, 33), (64, 2000, 40), (2000, 64, 40), (60, 60, 100)]
     seen = set()
     for (m, n, k), (layout, ta, tb) in zip(shapes * 2, itertools.cycle(
             itertools.product((H.COL, H.ROW), transposes(precision), transposes(precision)))):
         run_and_check(cuda, rng, precision, layout, ta, tb, m, n, k, 1.5, 0.5, 3, 5, 7, (5, 1, 3))
         seen.add(cb.last_kernel().rsplit("_", 1)[-1])
-    assert {"small", "medium"} <= seen
+    assert {"32x32", "64x64"} <= seen
     if precision < 100:
-        assert "large" in seen
+        assert {"128x128", "64x128"} <= seen
 
 
 @pytest.mark.parametrize("precision", (32, 64, 16))
@@ -197,9 +199,9 @@ def test_forcing_the_small_tile_family_through_override_parameters(cuda):
     dev = cuda.cuda.current_device()
     try:
         assert cb.OverrideParameters(dev, "GemmRoutine", 32, {"XGEMM_MIN_INDIRECT_SIZE": 4096}) == 0
-        run_and_check(cuda, rng, 32, H.COL, H.NO, H.NO, 300, 200, 100, 1.5, 0.5, expect_kernel="small")
+        run_and_check(cuda, rng, 32, H.COL, H.NO, H.NO, 300, 200, 100, 1.5, 0.5, expect_kernel="32x32")
         assert cb.OverrideParameters(dev, "GemmRoutine", 32, {"XGEMM_MIN_INDIRECT_SIZE": 0}) == 0
-        run_and_check(cuda, rng, 32, H.COL, H.NO, H.NO, 300, 200, 100, 1.5, 0.5, expect_kernel="medium")
+        run_and_check(cuda, rng, 32, H.COL, H.NO, H.NO, 300, 200, 100, 1.5, 0.5, reject_kernel="32x32")
     finally:
         cb.OverrideParameters(dev, "GemmRoutine", 32, {"XGEMM_MIN_INDIRECT_SIZE": 0})
 
