@@ -224,7 +224,10 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   const char* name = "none";
   cudaError_t err;
   switch (d.dtype) {
-    case 32: err = launch_simt_f32(d, stream, &name); break;
+    case 32:
+      err = launch_small_batched_f32(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);
+      break;
     case 64: err = launch_simt_f64(d, stream, &name); break;
     case 16:
       err = launch_tc_f16(d, stream, &name);
@@ -320,10 +323,12 @@ int prepare_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, s
   long long* h_c = h_b + batch_count;
   unsigned char* h_alpha = host_block + tables->off_block;
   unsigned char* h_beta = h_alpha + tables->sc_bytes;
+  bool offsets_aligned = true;
   for (size_t i = 0; i < batch_count; ++i) {
     h_a[i] = static_cast<long long>(swapped ? b_offsets[i] : a_offsets[i]);
     h_b[i] = static_cast<long long>(swapped ? a_offsets[i] : b_offsets[i]);
     h_c[i] = static_cast<long long>(c_offsets[i]);
+    if ((a_offsets[i] | b_offsets[i] | c_offsets[i]) & 3) offsets_aligned = false;
     double al[2], be[2];
     read_scalar(dtype, alphas, i, al);
     read_scalar(dtype, betas, i, be);
@@ -345,6 +350,7 @@ int prepare_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, s
       reinterpret_cast<double*>(h_beta)[2 * i + 1] = be[1];
     }
   }
+  d.tables_aligned4 = offsets_aligned ? 1 : 0;
   *out = d;
   return kSuccess;
 }
@@ -480,10 +486,12 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
   long long* h_c = h_b + batch_count;
   unsigned char* h_alpha = host.data() + off_block;
   unsigned char* h_beta = h_alpha + sc_bytes;
+  bool offsets_aligned = true;
   for (size_t i = 0; i < batch_count; ++i) {
     h_a[i] = static_cast<long long>(swapped ? b_offsets[i] : a_offsets[i]);
     h_b[i] = static_cast<long long>(swapped ? a_offsets[i] : b_offsets[i]);
     h_c[i] = static_cast<long long>(c_offsets[i]);
+    if ((a_offsets[i] | b_offsets[i] | c_offsets[i]) & 3) offsets_aligned = false;
     double al[2], be[2];
     read_scalar(dtype, alphas, i, al);
     read_scalar(dtype, betas, i, be);
@@ -505,6 +513,7 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
       reinterpret_cast<double*>(h_beta)[2 * i + 1] = be[1];
     }
   }
+  d.tables_aligned4 = offsets_aligned ? 1 : 0;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!async) {

@@ -36,6 +36,7 @@ struct GemmDesc {
   int is_conv;
   ConvGeom conv;
   int force_small;                // selection-table override: use the small-tile family
+  int tables_aligned4;            // every entry of the per-batch offset tables is a multiple of 4 elements
 };
 
 }  // namespace b200

@@ -74,6 +74,63 @@ def test_config4_small_batched_shapes(cuda, layout):
     check_strided(cuda, rng, 32, layout, H.NO, H.NO, 64, 128, 96, 65, 1.0, 1.0, lo=-1, hi=1)
 
 
+@pytest.mark.parametrize("layout", (H.COL, H.ROW))
+@pytest.mark.parametrize("ta,tb", ((H.NO, H.NO), (H.NO, H.YES), (H.YES, H.NO), (H.YES, H.YES)))
+def test_streaming_small_batched_kernel(cuda, layout, ta, tb):
+    """Large aligned batches of small fp32 problems take the cp.async streaming kernel; results must be bit-identical
+    to the reference-order oracle, like the generic kernel's."""
+    rng = np.random.default_rng(31)
+    for (m, n, k), batch, (alpha, beta), pad in (((32, 32, 32), 301, (1.0, 1.0), 0), ((16, 24, 20), 600, (1.5, 0.0), 4),
+                                                 ((64, 128, 96), 299, (1.0, 1.0), 0), ((60, 100, 64), 310, (0.5, 2.0), 8)):
+        g = strided_case(rng, 32, layout, ta, tb, m, n, k, batch, pad, 0, -1, 1)
+        da, db, dc = (H.to_device(cuda, 32, g[x]) for x in "abc")
+        cuda.cuda.synchronize()
+        st = cb.GemmStridedBatched(layout, ta, tb, m, n, k, alpha, da, 0, g["a_ld"], g["a_stride"], db, 0, g["b_ld"],
+                                   g["b_stride"], beta, dc, 0, g["c_ld"], g["c_stride"], batch)
+        assert st == cb.StatusCode.kSuccess
+        mm, nn = (m, n) if layout == H.COL else (n, m)   # extents after normalisation to a column-major C
+        eligible = mm % 4 == 0 and ((mm <= 32 and nn <= 32 and k <= 32) or (mm <= 64 and nn <= 128 and k <= 96))
+        assert cb.last_kernel().startswith("small_batched") == eligible, (cb.last_kernel(), m, n, k)
+        got = H.to_host(32, dc)
+        want = g["c"].copy()
+        for i in range(batch):
+            oracle.gemm(32, layout, ta, tb, m, n, k, alpha, g["a"], i * g["a_stride"], g["a_ld"], g["b"],
+                        i * g["b_stride"], g["b_ld"], beta, want, i * g["c_stride"], g["c_ld"])
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (m, n, k, layout, ta, tb)
+
+
+def test_streaming_kernel_with_per_batch_tables(cuda):
+    rng = np.random.default_rng(32)
+    m = n = k = 32
+    batch = 400
+    per = m * k
+    order = rng.permutation(batch)
+    a_offs = [int(o * per) for o in order]
+    b_offs = [int(o * per) for o in order[::-1]]
+    c_offs = [int(o * per) for o in rng.permutation(batch)]
+    a, b, c = (H.rand_buffer(rng, 32, batch * per, -1, 1) for _ in range(3))
+    alphas = [1.0 + 0.01 * i for i in range(batch)]
+    betas = [0.0 if i % 2 else 0.5 for i in range(batch)]
+    da, db, dc = (H.to_device(cuda, 32, x) for x in (a, b, c))
+    cuda.cuda.synchronize()
+    assert cb.GemmBatched(H.COL, H.NO, H.NO, m, n, k, alphas, da, a_offs, m, db, b_offs, k, betas, dc, c_offs, m,
+                          batch) == 0
+    assert cb.last_kernel().startswith("small_batched")
+    want = c.copy()
+    for i in range(batch):
+        oracle.gemm(32, H.COL, H.NO, H.NO, m, n, k, alphas[i], a, a_offs[i], m, b, b_offs[i], k, betas[i], want,
+                    c_offs[i], m)
+    assert np.array_equal(H.to_host(32, dc).view(np.uint8), want.view(np.uint8))
+    # one offset that is not a multiple of 4 elements sends the whole call to the generic kernel
+    a_offs[7] += 1
+    a2 = np.concatenate([a, np.zeros(4, dtype=np.float32)])
+    da2 = H.to_device(cuda, 32, a2)
+    cuda.cuda.synchronize()
+    assert cb.GemmBatched(H.COL, H.NO, H.NO, m, n, k, alphas, da2, a_offs, m, db, b_offs, k, betas, dc, c_offs, m,
+                          batch) == 0
+    assert cb.last_kernel().startswith("simt_")
+
+
 @pytest.mark.parametrize("m,n,k,batch", ((32, 32, 32, 8192), (64, 128, 96, 2048)))
 def test_config4_full_batch_equals_per_batch_calls(cuda, m, n, k, batch):
     torch = cuda
