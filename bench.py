@@ -402,10 +402,33 @@ def main():
     ms_per_step = ms / args.steps
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
-    # Dominant kernel alone (no collective), CUDA events on the launching stream: the roofline numerator.
+    # Dominant kernel alone (no collective), CUDA events on the launching stream: the roofline numerator. Kernels
+    # shorter than the host's per-call cost are replayed from a CUDA graph so that the GPU, not the Python caller,
+    # sets the pace; the plain back-to-back figure is kept beside it.
     def kernel_only():
-        launch(cb, w, t, stream)
+        launch(cb, w, t, torch.cuda.current_stream())
     kms = time_steps(torch, kernel_only, args.steps, 3, None) / args.steps
+    kms_plain = kms
+    timing = "cuda events, back-to-back launches"
+    if kms < 0.2:
+        try:
+            reps = 50
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                kernel_only()
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(reps):
+                        kernel_only()
+            torch.cuda.synchronize()
+            gms = time_steps(torch, graph.replay, max(3, args.steps // 4), 2, None) / max(3, args.steps // 4) / reps
+            if gms < kms:
+                kms = gms
+                timing = f"cuda events around a CUDA graph of {reps} launches"
+        except Exception as exc:  # capture is an optimisation of the measurement only
+            timing += f" (graph capture unavailable: {type(exc).__name__})"
     bound = w["bound"]
     if bound == "hbm":
         achieved = min_bytes_of(w) / (kms * 1e-3) / 1e9
@@ -427,6 +450,8 @@ def main():
                 "frac": achieved / peak, "traffic": None, "peak_source": src}
     roof["kernel"] = kernel_name
     roof["kernel_ms"] = kms
+    roof["kernel_ms_back_to_back"] = kms_plain
+    roof["timing"] = timing
     roof["algorithmic_bytes"] = min_bytes_of(w)
 
     # The same step under sustained load (about 1.5 s back to back): on a 1 kW part a dense tensor kernel runs into

@@ -185,7 +185,9 @@ void normalise(GemmDesc& d, int layout, int ta, int tb, size_t m, size_t n, size
 // ---- streams ------------------------------------------------------------------------------------------
 
 std::mutex g_stream_mutex;
-std::map<CUcontext, cudaStream_t> g_streams;
+// Keyed by the context's unique id where the driver offers one: a destroyed context's handle value can be reused
+// by a later context, and a stream of the dead context must not be handed out for the new one.
+std::map<unsigned long long, cudaStream_t> g_streams;
 
 // The library-owned non-blocking stream of the current context (one per context, created on first use).
 int private_stream(cudaStream_t* out) {
@@ -200,13 +202,18 @@ int private_stream(cudaStream_t* out) {
     r = drv.CtxGetCurrent(&ctx);
     if (r != CUDA_SUCCESS || !ctx) return CUDA_ERROR_INVALID_CONTEXT;
   }
+  unsigned long long key = reinterpret_cast<unsigned long long>(ctx);
+  if (drv.CtxGetId) {
+    unsigned long long id = 0;
+    if (drv.CtxGetId(ctx, &id) == CUDA_SUCCESS) key = (id << 1) | 1ull;  // odd keys: ids; even keys: handle values
+  }
   std::lock_guard<std::mutex> lock(g_stream_mutex);
-  auto it = g_streams.find(ctx);
+  auto it = g_streams.find(key);
   if (it == g_streams.end()) {
     cudaStream_t s = nullptr;
     const cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
     if (e != cudaSuccess) return static_cast<int>(e);
-    it = g_streams.emplace(ctx, s).first;
+    it = g_streams.emplace(key, s).first;
   }
   *out = it->second;
   return 0;

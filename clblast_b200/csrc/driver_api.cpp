@@ -14,6 +14,7 @@ DriverApi bind() {
   api.CtxGetCurrent = reinterpret_cast<decltype(api.CtxGetCurrent)>(sym("cuCtxGetCurrent"));
   api.CtxPushCurrent = reinterpret_cast<decltype(api.CtxPushCurrent)>(sym("cuCtxPushCurrent_v2"));
   api.CtxPopCurrent = reinterpret_cast<decltype(api.CtxPopCurrent)>(sym("cuCtxPopCurrent_v2"));
+  api.CtxGetId = reinterpret_cast<decltype(api.CtxGetId)>(sym("cuCtxGetId"));
   api.MemGetAddressRange = reinterpret_cast<decltype(api.MemGetAddressRange)>(sym("cuMemGetAddressRange_v2"));
   api.TensorMapEncodeTiled = reinterpret_cast<decltype(api.TensorMapEncodeTiled)>(sym("cuTensorMapEncodeTiled"));
   api.ok = api.CtxGetCurrent && api.CtxPushCurrent && api.CtxPopCurrent && api.MemGetAddressRange &&

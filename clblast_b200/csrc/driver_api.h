@@ -13,6 +13,7 @@ struct DriverApi {
   CUresult (*CtxGetCurrent)(CUcontext*);
   CUresult (*CtxPushCurrent)(CUcontext);
   CUresult (*CtxPopCurrent)(CUcontext*);
+  CUresult (*CtxGetId)(CUcontext, unsigned long long*);  // may be null on old drivers
   CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
   CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

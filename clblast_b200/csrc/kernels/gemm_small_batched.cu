@@ -261,14 +261,9 @@ struct SmallLauncher {
     constexpr int SMEM = GROUPS * SETS * L::SET_FLOATS * static_cast<int>(sizeof(float));
     static_assert(2 * SMEM <= 226 * 1024, "two CTAs must fit the shared memory of one SM");
     auto kernel = gemm_small_batched_kernel<BM, BN, KMAX, TM, TN, GROUPS, SETS, A_KC, B_KC>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-    if (!configured[dev]) {
+    {  // per-context attribute; contexts come and go, so it is set before every launch
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return e;
-      configured[dev] = true;
     }
     const long long ctas = (p.batch + GROUPS - 1) / GROUPS;
     const long long resident = 2LL * sm_count;  // two CTAs per SM

@@ -382,18 +382,17 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 16;
 
-  // Per-device one-time set-up: SM count and the opt-in to more than 48 KB of dynamic shared memory.
+  // SM count is cached per device; the opt-in to more than 48 KB of dynamic shared memory is per context, and
+  // contexts come and go, so it is simply repeated before every launch (a host-side attribute write).
   static int sm_counts[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) {
-    int count = 0;
-    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  {
     const cudaError_t e =
         cudaFuncSetAttribute(hgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    sm_counts[dev] = count;
   }
   const int sm_count = sm_counts[dev];
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
