@@ -88,6 +88,32 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, 2) gemm_small_
     c = p.c + (p.c_offs ? p.c_offs[t] : p.c_off + t * p.c_stride);
   };
 
+  // Copy plan of one operand: `rows` runs of `run` 16-byte chunks. Each thread walks the chunk list with stride NT;
+  // the (row, chunk) pair is advanced incrementally so the loop contains no integer division.
+  struct Plan {
+    int run, rows, row0, ch0, drow, dch;
+  };
+  auto make_plan = [&](int run, int rows) {
+    Plan q;
+    q.run = run; q.rows = rows;
+    q.row0 = tid / run; q.ch0 = tid % run;
+    q.drow = NT / run; q.dch = NT % run;
+    return q;
+  };
+  const Plan plan_a = make_plan((A_KC ? p.k : p.m) / 4, A_KC ? p.m : p.k);
+  const Plan plan_b = make_plan((B_KC ? p.k : p.n) / 4, B_KC ? p.n : p.k);
+  const Plan plan_c = make_plan(p.m / 4, p.n);
+
+  auto copy_operand = [&](const Plan& q, float* dst, int dst_ld, const float* src, long long src_ld) {
+    int r = q.row0, ch = q.ch0;
+    while (r < q.rows) {
+      cp_async16(dst + r * dst_ld + ch * 4, src + static_cast<long long>(r) * src_ld + ch * 4);
+      r += q.drow;
+      ch += q.dch;
+      if (ch >= q.run) { ch -= q.run; ++r; }
+    }
+  };
+
   auto prefetch = [&](long long t, int set) {
     if (t >= p.batch) return;
     const float *a, *b;
@@ -96,27 +122,9 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, 2) gemm_small_
     float* sa = my_sets + set * L::SET_FLOATS;
     float* sb = sa + L::A_FLOATS;
     float* sc = sb + L::B_FLOATS;
-    {  // A: rows of the stored matrix are contiguous in memory; 16-byte chunks
-      const int run = (A_KC ? p.k : p.m) / 4, rows = A_KC ? p.m : p.k;
-      for (int i = tid; i < run * rows; i += NT) {
-        const int r = i / run, ch = i - r * run;
-        cp_async16(sa + r * L::LDA + ch * 4, a + static_cast<long long>(r) * p.lda + ch * 4);
-      }
-    }
-    {
-      const int run = (B_KC ? p.k : p.n) / 4, rows = B_KC ? p.n : p.k;
-      for (int i = tid; i < run * rows; i += NT) {
-        const int r = i / run, ch = i - r * run;
-        cp_async16(sb + r * L::LDB + ch * 4, b + static_cast<long long>(r) * p.ldb + ch * 4);
-      }
-    }
-    if (p.need_c) {
-      const int run = p.m / 4;
-      for (int i = tid; i < run * p.n; i += NT) {
-        const int r = i / run, ch = i - r * run;
-        cp_async16(sc + r * BM + ch * 4, c + static_cast<long long>(r) * p.ldc + ch * 4);
-      }
-    }
+    copy_operand(plan_a, sa, L::LDA, a, p.lda);
+    copy_operand(plan_b, sb, L::LDB, b, p.ldb);
+    if (p.need_c) copy_operand(plan_c, sc, BM, c, p.ldc);
   };
 
   if (SETS == 2) {
