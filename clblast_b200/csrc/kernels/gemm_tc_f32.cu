@@ -1,0 +1,386 @@
+// SGEMM on the tensor cores with fp32-level accuracy: error-compensated 3xTF32 (TMA -> split into TF32 "big" and
+// "small" parts in shared memory -> three tcgen05.mma kind::tf32 per K step with fp32 accumulators in TMEM).
+//
+// Replaces, for large single-precision GEMMs with TMA-compatible operands, the reference's indirect path (Xgemm
+// kernel plus copy/pad/transpose kernels and temporaries: src/routines/level3/xgemm.cpp:101-222,
+// src/kernels/level3/xgemm_part3.opencl:53-305). Each fp32 operand x is split as x = hi + lo + e with
+// hi = tf32(x), lo = tf32(x - hi), both exactly representable in TF32 and |e| <= 2^-22 |x|; the product is formed as
+// lo_a*hi_b + hi_a*lo_b + hi_a*hi_b (the lo*lo term, <= 2^-22 relative, is dropped). Sums are fp32. The result is not
+// bit-identical to the k-ascending fused multiply-add chain of the CUDA-core kernel; its error against the fp64
+// product stays at the fp32 level (asserted in the tests: |x - r| <= 2^-20 * sum_k |a||b|).
+//
+// Both operand orientations are consumed where they lie: a K-contiguous operand is loaded as one K-major tile, an
+// M/N-contiguous operand as 32-wide MN-major column blocks; the split is element-wise and in place, so no transpose
+// ever happens. Requirements (host-checked): 16-byte aligned bases, leading dimensions multiples of 4 elements.
+//
+// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 epilogue, warps 6-9 split.
+// All waits are bounded; on expiry a code is left in g_tc32_status and the CTA drains and exits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "../driver_api.h"
+#include "launchers.h"
+#include "tc_common.cuh"
+
+namespace b200 {
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;
+constexpr int BK = 32;  // 32 floats = one 128-byte swizzle row
+constexpr int UMMA_K = 8;
+constexpr int NUM_THREADS = 320;
+constexpr int TMEM_COLS = 512;
+
+__device__ unsigned int g_tc32_status[4];
+
+struct Tc32Params {
+  float* c;
+  long long ldc;
+  int m, n, k;
+  int tiles_m, tiles_n, k_blocks;
+  float alpha, beta;
+  int raster_group;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // main (raw -> hi in place) and lo copies
+  static constexpr int STAGES = (BN == 256) ? 2 : 3;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ void tile_coords(const Tc32Params& p, int tile, int& tm, int& tn) {
+  const int per_group = p.raster_group * p.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * p.raster_group;
+  const int rows = min(p.raster_group, p.tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
+// A_MN / B_MN: the operand is M/N-contiguous (MN-major tiles) instead of K-contiguous (K-major tiles).
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const Tc32Params p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * C::STAGE_BYTES);
+  const uint32_t bar_base = smem_u32(bars);
+  // [0,S) raw data landed, [S,2S) split done, [2S,3S) stage free, then 2 accumulator-full, 2 accumulator-free
+  auto raw_full = [&](int s) { return bar_base + 8u * s; };
+  auto split_full = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto stage_free = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (3 * STAGES + a); };
+  auto acc_free = [&](int a) { return bar_base + 8u * (3 * STAGES + 2 + a); };
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
+  volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(raw_full(s), 1);
+      mbar_init(split_full(s), 4);
+      mbar_init(stage_free(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full(a), 1);
+      mbar_init(acc_free(a), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // stage layout: A main | B main | A lo | B lo
+  auto a_main = [&](int s) { return tiles_base + s * C::STAGE_BYTES; };
+  auto b_main = [&](int s) { return a_main(s) + C::A_BYTES; };
+  auto a_lo = [&](int s) { return b_main(s) + C::B_BYTES; };
+  auto b_lo = [&](int s) { return a_lo(s) + C::A_BYTES; };
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_status)) { ok = false; break; }
+          mbar_arrive_expect_tx(raw_full(stage), C::A_BYTES + C::B_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 32; ++j)
+              tma_load_2d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, kb * BK);
+          } else {
+            tma_load_2d(a_main(stage), &map_a, raw_full(stage), kb * BK, tm * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j)
+              tma_load_2d(b_main(stage) + j * 4096, &map_b, raw_full(stage), tn * BN + j * 32, kb * BK);
+          } else {
+            tma_load_2d(b_main(stage), &map_b, raw_full(stage), kb * BK, tn * BN);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const int pending = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < pending; ++i) {
+          const long long start = clock64();
+          int s = stage - 1 - i;
+          if (s < 0) s += STAGES;
+          const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+          while (!mbar_try_wait(raw_full(s), par) && clock64() - start < kWaitCycles / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 2, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(acc_free(acc), acc_phase ^ 1u, abort_flag, 2u, g_tc32_status)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * (TMEM_COLS / 2));
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, g_tc32_status)) { ok = false; break; }
+          tcgen05_fence_after();
+          // K-major: rows of 128 B along K (16-byte-chunk swizzle), advance 8 floats = 32 B per MMA.
+          // MN-major: one 128-byte row per k (32-byte-chunk swizzle, atoms of four k = 512 B), eight k = 1024 B per
+          // MMA, 32-wide column blocks 4096 B apart.
+          const uint32_t a_lbo = A_MN ? 4096u : 16u, b_lbo = B_MN ? 4096u : 16u;
+          const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+          const uint32_t a_type = A_MN ? kLayoutSw128Base32 : kLayoutSw128, b_type = B_MN ? kLayoutSw128Base32 : kLayoutSw128;
+          const uint32_t a_step = A_MN ? 1024u : 32u, b_step = B_MN ? 1024u : 32u;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint64_t a_hi = smem_desc(a_main(stage) + ks * a_step, a_lbo, a_sbo, a_type);
+            const uint64_t a_sm = smem_desc(a_lo(stage) + ks * a_step, a_lbo, a_sbo, a_type);
+            const uint64_t b_hi = smem_desc(b_main(stage) + ks * b_step, b_lbo, b_sbo, b_type);
+            const uint64_t b_sm = smem_desc(b_lo(stage) + ks * b_step, b_lbo, b_sbo, b_type);
+            umma_tf32(d_tmem, a_sm, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);  // small terms first
+            umma_tf32(d_tmem, a_hi, b_sm, idesc, 1u);
+            umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+          }
+          umma_commit(stage_free(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full(acc));
+      }
+    }
+  } else if (warp < 6) {
+    // ---- epilogue: warps 2..5 ----
+    const int quad = warp & 3;
+    int local = 0;
+    bool ok = true;
+    const bool use_beta = p.beta != 0.f;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      ok = mbar_wait(acc_full(acc), acc_phase, abort_flag, 4u, g_tc32_status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const bool row_ok = row < p.m;
+      const int col0 = tn * BN;
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * (TMEM_COLS / 2));
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        if (col0 + cb * 32 >= p.n) break;
+        uint32_t r[32];
+        tmem_ld_32cols(t_row + cb * 32, r);
+        if (row_ok) {
+          float* cptr = p.c + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + cb * 32 + j < p.n) {
+              float v = __fmul_rn(p.alpha, __uint_as_float(r[j]));
+              if (use_beta) v = fmaf(p.beta, cptr[static_cast<long long>(j) * p.ldc], v);
+              cptr[static_cast<long long>(j) * p.ldc] = v;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_free(acc));
+    }
+  } else {
+    // ---- split: warps 6..9 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
+    const int t = threadIdx.x - 6 * 32;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;  // A and B main tiles are adjacent, so are the lo tiles
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES);
+        float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+#pragma unroll 4
+        for (int c = t; c < CHUNKS; c += 128) {
+          const float4 x = main_ptr[c];
+          float4 hi, lo;
+          hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
+          lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z); lo.w = to_tf32(x.w - hi.w);
+          // infinities and NaNs stay in the big part only (inf - inf would poison the small part)
+          if ((__float_as_uint(hi.x) & 0x7f800000u) == 0x7f800000u) lo.x = 0.f;
+          if ((__float_as_uint(hi.y) & 0x7f800000u) == 0x7f800000u) lo.y = 0.f;
+          if ((__float_as_uint(hi.z) & 0x7f800000u) == 0x7f800000u) lo.z = 0.f;
+          if ((__float_as_uint(hi.w) & 0x7f800000u) == 0x7f800000u) lo.w = 0.f;
+          main_ptr[c] = hi;
+          lo_ptr[c] = lo;
+        }
+        fence_proxy_async();  // the tensor cores read these tiles through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(split_full(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// K-contiguous operand: 2-D map {K, rows}, box {32, box_rows}. M/N-contiguous operand: map {rows, K}, box {32, 32}.
+bool encode_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, bool mn_contig,
+                int box_rows) {
+  const DriverApi& drv = driver_api();
+  if (!drv.ok) return false;
+  cuuint64_t dims[2];
+  cuuint32_t box[2];
+  if (mn_contig) {
+    dims[0] = static_cast<cuuint64_t>(rows); dims[1] = static_cast<cuuint64_t>(k);
+    box[0] = 32; box[1] = 32;
+  } else {
+    dims[0] = static_cast<cuuint64_t>(k); dims[1] = static_cast<cuuint64_t>(rows);
+    box[0] = 32; box[1] = static_cast<cuuint32_t>(box_rows);
+  }
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  const cuuint32_t estr[2] = {1, 1};
+  // M/N-major 32-bit operands must sit in shared memory with the 32-byte-chunk flavour of the 128-byte swizzle.
+  const CUtensorMapSwizzle swizzle = mn_contig ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  return drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid,
+                           cudaStream_t stream) {
+  auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN>;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma, mb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t tc_f32_status(unsigned int out[4], bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc32_status, sizeof(unsigned int) * 4);
+  if (e == cudaSuccess && clear && out[0] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_tc32_status, zero, sizeof(zero));
+  }
+  return e;
+}
+
+cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
+  if (d.dtype != 32 || d.is_conv || d.batch != 1 || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  // Static selection: the tensor-core path pays off once there are enough 128x256 tiles and K blocks to fill the
+  // pipeline; smaller problems keep the k-ascending CUDA-core kernel. B200BLAS_SGEMM=ffma forces the latter.
+  static const bool forced_ffma = [] {
+    const char* v = std::getenv("B200BLAS_SGEMM");
+    return v != nullptr && std::strcmp(v, "ffma") == 0;
+  }();
+  if (forced_ffma) return cudaErrorNotSupported;
+  if (d.m < 256 || d.n < 256 || d.k < 128) return cudaErrorNotSupported;
+  if (static_cast<double>(d.m) * d.n * d.k < 134217728.0) return cudaErrorNotSupported;  // 512^3
+  if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
+  const float* a = static_cast<const float*>(d.a) + d.a_off;
+  const float* b = static_cast<const float*>(d.b) + d.b_off;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
+  if ((d.lda % 4) || (d.ldb % 4)) return cudaErrorNotSupported;
+  if (d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40)) return cudaErrorNotSupported;
+
+  constexpr int BN = 256;
+  CUtensorMap map_a, map_b;
+  if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig, BM)) return cudaErrorNotSupported;
+  if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, BN)) return cudaErrorNotSupported;
+
+  Tc32Params p;
+  p.c = static_cast<float*>(d.c) + d.c_off;
+  p.ldc = d.ldc;
+  p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
+  p.tiles_m = static_cast<int>((d.m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((d.n + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
+  p.alpha = static_cast<float>(d.alpha[0]);
+  p.beta = static_cast<float>(d.beta[0]);
+  p.raster_group = 16;
+
+  static int sm_counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
+  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  const int grid = static_cast<int>(tiles < sm_counts[dev] ? tiles : sm_counts[dev]);
+
+  *name = "tc_f32_3xtf32_128x256x32";
+  const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
+  if (a_mn) {
+    return b_mn ? launch_variant<BN, true, true>(map_a, map_b, p, grid, stream)
+                : launch_variant<BN, true, false>(map_a, map_b, p, grid, stream);
+  }
+  return b_mn ? launch_variant<BN, false, true>(map_a, map_b, p, grid, stream)
+              : launch_variant<BN, false, false>(map_a, map_b, p, grid, stream);
+}
+
+}  // namespace b200

@@ -19,6 +19,10 @@ cudaError_t launch_simt_c64(const GemmDesc& d, cudaStream_t stream, const char**
 // the call does not meet the kernel's layout and alignment requirements; the caller then uses the CUDA-core path.
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name);
 
+// Tensor-core SGEMM (error-compensated 3xTF32). Same contract as launch_tc_f16.
+cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
+cudaError_t tc_f32_status(unsigned int out[4], bool clear);
+
 // Streaming kernel for large batches of small fp32 problems (cp.async double buffering across the batch). Returns
 // cudaErrorNotSupported without launching when the call does not meet its shape and alignment requirements.
 cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, const char** name);

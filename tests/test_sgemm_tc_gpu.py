@@ -1,0 +1,101 @@
+"""The tensor-core SGEMM kernel (error-compensated 3xTF32 on tcgen05) against the fp64 oracle.
+
+Tolerance: the reference's fp32 margins (relative 5e-3 or absolute 1e-3, test/correctness/tester.cpp:29-69) and the
+fp32-quality bound |x - r| <= 2^-20 * (|alpha| * sum_k|a||b| + |beta||c|); the kernel is not bit-identical to the
+k-ascending reference order, the CUDA-core kernel (B200BLAS_SGEMM=ffma, or any smaller problem) is."""
+import itertools
+
+import numpy as np
+import pytest
+
+import clblast_b200 as cb
+from oracle import cpu_oracle as oracle
+from tests import harness as H
+
+pytestmark = pytest.mark.gpu
+
+
+def run_tc32(torch, rng, layout, ta, tb, m, n, k, alpha, beta, offs=(0, 0, 0), pad=(0, 0, 0), expect_tc=True):
+    case = H.gemm_case(rng, 32, layout, ta, tb, m, n, k, offs[0], offs[1], offs[2], pad, lo=-1, hi=1,
+                       poison_c=(beta == 0))
+    da, db, dc = (H.to_device(torch, 32, case[x]) for x in "abc")
+    torch.cuda.synchronize()
+    st = cb.Gemm(layout, ta, tb, m, n, k, alpha, da, offs[0], case["a_ld"], db, offs[1], case["b_ld"], beta, dc, offs[2],
+                 case["c_ld"], precision=32)
+    assert st == cb.StatusCode.kSuccess, st
+    assert cb.last_kernel().startswith("tc_f32") == expect_tc, cb.last_kernel()
+    got = H.to_host(32, dc)
+    c_in = case["c"].copy()
+    if beta == 0:
+        c_in[:] = 0
+    want = oracle.gemm_f64(32, layout, ta, tb, m, n, k, alpha, case["a"], offs[0], case["a_ld"], case["b"], offs[1],
+                           case["b_ld"], beta, c_in, offs[2], case["c_ld"])
+    mask = H.c_mask(layout, m, n, offs[2], case["c_ld"], case["c"].size)
+    worst = H.check_against_oracle(32, got, want, mask, case["c"])
+    # data is U[-1,1]: sum_k|a||b| <= k
+    assert worst <= 2.0 ** -20 * (abs(alpha) * k + abs(beta)), worst / (abs(alpha) * k + abs(beta))
+    return worst
+
+
+ALL = list(itertools.product((H.COL, H.ROW), (H.NO, H.YES), (H.NO, H.YES)))
+
+
+@pytest.mark.parametrize("layout,ta,tb", ALL)
+def test_all_operand_orientations(cuda, layout, ta, tb):
+    rng = np.random.default_rng(1)
+    run_tc32(cuda, rng, layout, ta, tb, 512, 512, 512, 1.0, 0.0)
+    run_tc32(cuda, rng, layout, ta, tb, 768, 1024, 256, 1.5, 0.5)
+
+
+@pytest.mark.parametrize("layout,ta,tb", ALL)
+def test_ragged_edges_k_tail_offsets(cuda, layout, ta, tb):
+    rng = np.random.default_rng(2)
+    run_tc32(cuda, rng, layout, ta, tb, 1000, 1111, 520, 1.5, 0.5, offs=(4, 8, 3), pad=(4, 8, 1))
+    run_tc32(cuda, rng, layout, ta, tb, 700, 900, 300, -0.5, 0.0, pad=(12, 0, 5))
+
+
+def test_unaligned_or_small_problems_keep_the_cuda_core_kernel(cuda):
+    rng = np.random.default_rng(3)
+    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 600, 600, 600, 1.0, 0.0, pad=(1, 0, 0), expect_tc=False)   # lda % 4 != 0
+    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 600, 600, 600, 1.0, 0.0, offs=(2, 0, 0), expect_tc=False)  # base not 16 B
+    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 200, 200, 200, 1.0, 0.0, expect_tc=False)                  # too small
+
+
+def test_infinities_do_not_turn_into_nan(cuda):
+    torch = cuda
+    n = 512
+    a = torch.rand(n * n, device="cuda") + 0.5
+    b = torch.rand(n * n, device="cuda") + 0.5
+    a[5] = float("inf")  # column-major A: element (5, 0)
+    c = torch.zeros(n * n, device="cuda")
+    torch.cuda.synchronize()
+    assert cb.Gemm(H.COL, H.NO, H.NO, n, n, n, 1.0, a, 0, n, b, 0, n, 0.0, c, 0, n) == 0
+    assert cb.last_kernel().startswith("tc_f32")
+    row5 = c.view(n, n)[:, 5]  # C(5, j) for all j
+    assert torch.isinf(row5).all() and not torch.isnan(c).any()
+
+
+@pytest.mark.parametrize("n", (4096, 8192))
+def test_config2_large_squares_sampled(cuda, n):
+    torch = cuda
+    g = torch.Generator(device="cuda").manual_seed(n)
+    ld = n + 16
+    a = torch.rand(ld * n, generator=g, device="cuda") * 2 - 1
+    b = torch.rand(ld * n, generator=g, device="cuda") * 2 - 1
+    c0 = torch.rand(ld * n, generator=g, device="cuda") * 2 - 1
+    rs = np.random.default_rng(n)
+    rows, cols = rs.integers(0, n, 4096), rs.integers(0, n, 4096)
+    ah, bh, ch = a.cpu().numpy(), b.cpu().numpy(), c0.cpu().numpy()
+    for ta, tb in itertools.product((H.NO, H.YES), repeat=2):
+        c = c0.clone()
+        torch.cuda.synchronize()
+        assert cb.Gemm(H.COL, ta, tb, n, n, n, 1.5, a, 0, ld, b, 0, ld, 0.5, c, 0, ld) == 0
+        assert cb.last_kernel().startswith("tc_f32")
+        want, mag = oracle.gemm_f64_sampled(32, H.COL, ta, tb, n, 1.5, ah, 0, ld, bh, 0, ld, rows, cols)
+        want = want + 0.5 * ch[cols * ld + rows].astype(np.float64)
+        got = c.cpu().numpy()[cols * ld + rows].astype(np.float64)
+        bad, _ = oracle.count_mismatches(32, got, want)
+        assert bad == 0
+        assert (np.abs(got - want) / (1.5 * mag + 0.5)).max() < 2.0 ** -20
+        # the padding between columns is untouched
+        assert torch.equal(c.view(n, ld)[:, n:], c0.view(n, ld)[:, n:])
