@@ -5,15 +5,19 @@
 // kernel plus copy/pad/transpose kernels and temporaries: src/routines/level3/xgemm.cpp:101-222,
 // src/kernels/level3/xgemm_part3.opencl:53-305). Each fp32 operand x is split as x = hi + lo + e with
 // hi = tf32(x), lo = tf32(x - hi), both exactly representable in TF32 and |e| <= 2^-22 |x|; the product is formed as
-// lo_a*hi_b + hi_a*lo_b + hi_a*hi_b (the lo*lo term, <= 2^-22 relative, is dropped). Sums are fp32. The result is not
-// bit-identical to the k-ascending fused multiply-add chain of the CUDA-core kernel; its error against the fp64
-// product stays at the fp32 level (asserted in the tests: |x - r| <= 2^-20 * sum_k |a||b|).
+// lo_a*hi_b + hi_a*lo_b + hi_a*hi_b (the lo*lo term, <= 2^-22 relative, is dropped). The tensor cores add into
+// their fp32 accumulators with truncation, which over thousands of accumulations costs several bits, so they only
+// accumulate over a short chunk of K (CHUNK_KB blocks of 32) into one of two TMEM partial buffers; eight
+// "drain" warps then add each finished partial into fp32 register accumulators with round-to-nearest while the
+// tensor cores fill the other buffer. The result is not bit-identical to the k-ascending fused multiply-add chain
+// of the CUDA-core kernel; its error against the fp64 product stays at the fp32 level (asserted in the tests).
 //
 // Both operand orientations are consumed where they lie: a K-contiguous operand is loaded as one K-major tile, an
 // M/N-contiguous operand as 32-wide MN-major column blocks; the split is element-wise and in place, so no transpose
 // ever happens. Requirements (host-checked): 16-byte aligned bases, leading dimensions multiples of 4 elements.
 //
-// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 epilogue, warps 6-9 split.
+// Roles (512 threads, four warpgroups with re-balanced register budgets): warp 0 TMA producer, warp 1 MMA issuer
+// and TMEM owner (warps 2-3 idle), warps 4-7 split, warps 8-15 drain + epilogue.
 // All waits are bounded; on expiry a code is left in g_tc32_status and the CTA drains and exits.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -35,7 +39,8 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int BK = 32;  // 32 floats = one 128-byte swizzle row
 constexpr int UMMA_K = 8;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 512;
+constexpr int CHUNK_KB = 2;  // K blocks accumulated inside the tensor cores before a partial is drained
 constexpr int TMEM_COLS = 512;
 
 __device__ unsigned int g_tc32_status[4];
@@ -81,12 +86,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
   uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * C::STAGE_BYTES);
   const uint32_t bar_base = smem_u32(bars);
-  // [0,S) raw data landed, [S,2S) split done, [2S,3S) stage free, then 2 accumulator-full, 2 accumulator-free
+  // [0,S) raw data landed, [S,2S) split done, [2S,3S) stage free, then 2 partial-full, 2 partial-free
   auto raw_full = [&](int s) { return bar_base + 8u * s; };
   auto split_full = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto stage_free = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-  auto acc_full = [&](int a) { return bar_base + 8u * (3 * STAGES + a); };
-  auto acc_free = [&](int a) { return bar_base + 8u * (3 * STAGES + 2 + a); };
+  auto part_full = [&](int a) { return bar_base + 8u * (3 * STAGES + a); };
+  auto part_free = [&](int a) { return bar_base + 8u * (3 * STAGES + 2 + a); };
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
   volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -101,8 +106,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(stage_free(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(acc_full(a), 1);
-      mbar_init(acc_free(a), 4);
+      mbar_init(part_full(a), 1);
+      mbar_init(part_free(a), 8);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -119,6 +124,9 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   auto a_lo = [&](int s) { return b_main(s) + C::B_BYTES; };
   auto b_lo = [&](int s) { return a_lo(s) + C::A_BYTES; };
 
+  // Register budgets are re-balanced per warpgroup: producers need few, drain warps hold 128 accumulators each.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ---- TMA producer ----
     if (lane == 0) {
@@ -167,84 +175,98 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       constexpr uint32_t idesc = make_idesc(BM, BN, 2, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
-      int local = 0;
+      int chunk_index = 0;  // running count of partials produced by this CTA
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(acc_free(acc), acc_phase ^ 1u, abort_flag, 2u, g_tc32_status)) { ok = false; break; }
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * (TMEM_COLS / 2));
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, g_tc32_status)) { ok = false; break; }
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, ++chunk_index) {
+          const int part = chunk_index & 1;
+          const uint32_t part_phase = (chunk_index >> 1) & 1u;
+          if (!mbar_wait(part_free(part), part_phase ^ 1u, abort_flag, 2u, g_tc32_status)) { ok = false; break; }
           tcgen05_fence_after();
-          // K-major: rows of 128 B along K (16-byte-chunk swizzle), advance 8 floats = 32 B per MMA.
-          // MN-major: one 128-byte row per k (32-byte-chunk swizzle, atoms of four k = 512 B), eight k = 1024 B per
-          // MMA, 32-wide column blocks 4096 B apart.
-          const uint32_t a_lbo = A_MN ? 4096u : 16u, b_lbo = B_MN ? 4096u : 16u;
-          const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
-          const uint32_t a_type = A_MN ? kLayoutSw128Base32 : kLayoutSw128, b_type = B_MN ? kLayoutSw128Base32 : kLayoutSw128;
-          const uint32_t a_step = A_MN ? 1024u : 32u, b_step = B_MN ? 1024u : 32u;
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(part * (TMEM_COLS / 2));
+          const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, g_tc32_status)) { ok = false; break; }
+            tcgen05_fence_after();
+            // K-major: rows of 128 B along K (16-byte-chunk swizzle), advance 8 floats = 32 B per MMA.
+            // MN-major: one 128-byte row per k (32-byte-chunk swizzle, atoms of four k = 512 B), eight k = 1024 B
+            // per MMA, 32-wide column blocks 4096 B apart.
+            const uint32_t a_lbo = A_MN ? 4096u : 16u, b_lbo = B_MN ? 4096u : 16u;
+            const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+            const uint32_t a_type = A_MN ? kLayoutSw128Base32 : kLayoutSw128;
+            const uint32_t b_type = B_MN ? kLayoutSw128Base32 : kLayoutSw128;
+            const uint32_t a_step = A_MN ? 1024u : 32u, b_step = B_MN ? 1024u : 32u;
 #pragma unroll
-          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-            const uint64_t a_hi = smem_desc(a_main(stage) + ks * a_step, a_lbo, a_sbo, a_type);
-            const uint64_t a_sm = smem_desc(a_lo(stage) + ks * a_step, a_lbo, a_sbo, a_type);
-            const uint64_t b_hi = smem_desc(b_main(stage) + ks * b_step, b_lbo, b_sbo, b_type);
-            const uint64_t b_sm = smem_desc(b_lo(stage) + ks * b_step, b_lbo, b_sbo, b_type);
-            umma_tf32(d_tmem, a_sm, b_hi, idesc, (kb | ks) != 0 ? 1u : 0u);  // small terms first
-            umma_tf32(d_tmem, a_hi, b_sm, idesc, 1u);
-            umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+              const uint64_t a_hi = smem_desc(a_main(stage) + ks * a_step, a_lbo, a_sbo, a_type);
+              const uint64_t a_sm = smem_desc(a_lo(stage) + ks * a_step, a_lbo, a_sbo, a_type);
+              const uint64_t b_hi = smem_desc(b_main(stage) + ks * b_step, b_lbo, b_sbo, b_type);
+              const uint64_t b_sm = smem_desc(b_lo(stage) + ks * b_step, b_lbo, b_sbo, b_type);
+              umma_tf32(d_tmem, a_sm, b_hi, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);  // small terms first
+              umma_tf32(d_tmem, a_hi, b_sm, idesc, 1u);
+              umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+            }
+            umma_commit(stage_free(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
-          umma_commit(stage_free(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (ok) umma_commit(part_full(part));  // this partial is complete
         }
-        if (ok) umma_commit(acc_full(acc));
       }
     }
-  } else if (warp < 6) {
-    // ---- epilogue: warps 2..5 ----
+  }
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+    // ---- drain + epilogue: warps 8..15. Warp w reads TMEM lanes [32*(w%4), +32) and columns [128*h, +128) ----
     const int quad = warp & 3;
-    int local = 0;
+    const int half = (warp - 8) >> 2;
+    int chunk_index = 0;
     bool ok = true;
     const bool use_beta = p.beta != 0.f;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm, tn;
       tile_coords(p, tile, tm, tn);
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1u;
-      ok = mbar_wait(acc_full(acc), acc_phase, abort_flag, 4u, g_tc32_status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const int row = tm * BM + quad * 32 + lane;
-      const bool row_ok = row < p.m;
-      const int col0 = tn * BN;
-      const uint32_t t_row =
-          tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * (TMEM_COLS / 2));
-#pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
-        if (col0 + cb * 32 >= p.n) break;
-        uint32_t r[32];
-        tmem_ld_32cols(t_row + cb * 32, r);
-        if (row_ok) {
-          float* cptr = p.c + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
+      float acc[BN / 2];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + cb * 32 + j < p.n) {
-              float v = __fmul_rn(p.alpha, __uint_as_float(r[j]));
-              if (use_beta) v = fmaf(p.beta, cptr[static_cast<long long>(j) * p.ldc], v);
-              cptr[static_cast<long long>(j) * p.ldc] = v;
-            }
+      for (int j = 0; j < BN / 2; ++j) acc[j] = 0.f;
+      for (int kb0 = 0; kb0 < p.k_blocks; kb0 += CHUNK_KB, ++chunk_index) {
+        const int part = chunk_index & 1;
+        const uint32_t part_phase = (chunk_index >> 1) & 1u;
+        ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, g_tc32_status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                               static_cast<uint32_t>(part * (TMEM_COLS / 2) + half * (BN / 2));
+#pragma unroll
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint32_t r[32];
+          tmem_ld_32cols(t_row + cb * 32, r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[cb * 32 + j] += __uint_as_float(r[j]);  // round-to-nearest adds
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(part_free(part));
+      }
+      if (!ok) break;
+      const int row = tm * BM + quad * 32 + lane;
+      const int col0 = tn * BN + half * (BN / 2);
+      if (row < p.m) {
+        float* cptr = p.c + static_cast<long long>(col0) * p.ldc + row;
+#pragma unroll
+        for (int j = 0; j < BN / 2; ++j) {
+          if (col0 + j < p.n) {
+            float v = __fmul_rn(p.alpha, acc[j]);
+            if (use_beta) v = fmaf(p.beta, cptr[static_cast<long long>(j) * p.ldc], v);
+            cptr[static_cast<long long>(j) * p.ldc] = v;
           }
         }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_free(acc));
     }
   } else {
-    // ---- split: warps 6..9 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
-    const int t = threadIdx.x - 6 * 32;  // 0..127
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    // ---- split: warps 4..7 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
+    const int t = threadIdx.x - 4 * 32;  // 0..127
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;

@@ -50,7 +50,7 @@ def test_all_operand_orientations(cuda, layout, ta, tb):
 @pytest.mark.parametrize("layout,ta,tb", ALL)
 def test_ragged_edges_k_tail_offsets(cuda, layout, ta, tb):
     rng = np.random.default_rng(2)
-    run_tc32(cuda, rng, layout, ta, tb, 1000, 1111, 520, 1.5, 0.5, offs=(4, 8, 3), pad=(4, 8, 1))
+    run_tc32(cuda, rng, layout, ta, tb, 1000, 1112, 520, 1.5, 0.5, offs=(4, 8, 3), pad=(4, 8, 1))
     run_tc32(cuda, rng, layout, ta, tb, 700, 900, 300, -0.5, 0.0, pad=(12, 0, 5))
 
 
