@@ -215,10 +215,35 @@ struct TileStager {
     }
   }
 
-  // Convolution flavour of `fetch` for op(A): x indexes output pixels, k indexes (channel, kh, kw).
+  // Convolution flavour of `fetch` for op(A): x indexes output pixels, k indexes (channel, kh, kw). The pixel part of
+  // the address (top-left tap of every output pixel this thread stages) does not change along K, so it is computed
+  // once per tile by conv_pixels(); pixels outside the tile get a row far outside the image and load as zero.
+  static __device__ __forceinline__ void conv_pixels(int (&hi0)[NV][VEC], int (&wi0)[NV][VEC], const ConvGeom& g,
+                                                     long long x0, long long x_rem, int tid) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      int x, kk;
+      coords(i, tid, x, kk);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const int xe = x + j;
+        if (xe < x_rem) {
+          const int p = static_cast<int>(x0) + xe;
+          const int ho = p / g.out_w;
+          const int wo = p - ho * g.out_w;
+          hi0[i][j] = ho * g.stride_h - g.pad_h;
+          wi0[i][j] = wo * g.stride_w - g.pad_w;
+        } else {
+          hi0[i][j] = -(1 << 28);
+          wi0[i][j] = 0;
+        }
+      }
+    }
+  }
+
   static __device__ __forceinline__ void fetch_conv(T (&reg)[NV][VEC], const T* __restrict__ image, const ConvGeom& g,
-                                                    long long x0, long long k0, long long x_rem, long long k_rem,
-                                                    int tid) {
+                                                    const int (&hi0)[NV][VEC], const int (&wi0)[NV][VEC], long long k0,
+                                                    long long k_rem, int tid) {
     static_assert(!KCONTIG, "the convolution loader walks output pixels fastest");
     const int khw = g.kernel_h * g.kernel_w;
 #pragma unroll
@@ -234,21 +259,16 @@ struct TileStager {
         kh_id = g.kernel_h - 1 - kh_id;
         kw_id = g.kernel_w - 1 - kw_id;
       }
-      const int h_base = kh_id * g.dil_h - g.pad_h;
-      const int w_base = kw_id * g.dil_w - g.pad_w;
+      const int dh = kh_id * g.dil_h;
+      const int dw = kw_id * g.dil_w;
       const T* plane = image + static_cast<long long>(c_id) * g.height * g.width;
+      const bool k_ok = kk < k_rem;
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
-        const int xe = x + j;
+        const int hi = hi0[i][j] + dh;
+        const int wi = wi0[i][j] + dw;
         T val = Tr::st(Tr::zero());
-        if (xe < x_rem && kk < k_rem) {
-          const int p = static_cast<int>(x0) + xe;
-          const int ho = p / g.out_w;
-          const int wo = p - ho * g.out_w;
-          const int hi = h_base + ho * g.stride_h;
-          const int wi = w_base + wo * g.stride_w;
-          if (hi >= 0 && hi < g.height && wi >= 0 && wi < g.width) val = plane[hi * g.width + wi];
-        }
+        if (k_ok && hi >= 0 && hi < g.height && wi >= 0 && wi < g.width) val = plane[hi * g.width + wi];
         reg[i][j] = val;
       }
     }
@@ -336,9 +356,13 @@ gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
     T ra[StA::NV][Tr::VEC];
     T rb[StB::NV][Tr::VEC];
 
+    int conv_h0[CONV ? StA::NV : 1][CONV ? Tr::VEC : 1];
+    int conv_w0[CONV ? StA::NV : 1][CONV ? Tr::VEC : 1];
+    if constexpr (CONV) StA::conv_pixels(conv_h0, conv_w0, p.conv, m0, m_rem, tid);
+
     auto fetch_tiles = [&](long long k0) {
       if constexpr (CONV) {
-        StA::fetch_conv(ra, a_base, p.conv, m0, k0, m_rem, p.k - k0, tid);
+        StA::fetch_conv(ra, a_base, p.conv, conv_h0, conv_w0, k0, p.k - k0, tid);
       } else {
         StA::fetch(ra, a_base, p.lda, m0, k0, m_rem, p.k - k0, a_vec_ok, tid);
       }

@@ -16,8 +16,8 @@
 // M/N-contiguous operand as 32-wide MN-major column blocks; the split is element-wise and in place, so no transpose
 // ever happens. Requirements (host-checked): 16-byte aligned bases, leading dimensions multiples of 4 elements.
 //
-// Roles (512 threads, four warpgroups with re-balanced register budgets): warp 0 TMA producer, warp 1 MMA issuer
-// and TMEM owner (warps 2-3 idle), warps 4-7 split, warps 8-15 drain + epilogue.
+// Roles (640 threads, five warpgroups with re-balanced register budgets): warp 0 TMA producer, warp 1 MMA issuer
+// and TMEM owner (warps 2-3 idle), warps 4-11 split, warps 12-19 drain + epilogue.
 // All waits are bounded; on expiry a code is left in g_tc32_status and the CTA drains and exits.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -39,7 +39,11 @@ using namespace tc;
 constexpr int BM = 128;
 constexpr int BK = 32;  // 32 floats = one 128-byte swizzle row
 constexpr int UMMA_K = 8;
-constexpr int NUM_THREADS = 512;
+constexpr int NUM_THREADS = 640;
+// Register re-balancing must stay inside the CTA's own allocation (threads x registers at launch), otherwise the
+// increase waits forever: 128 producer threads x 40 + 256 split threads x 56 + 256 drain threads x 160.
+constexpr int LAUNCH_REGS = 96;  // floor(65536 / 640) rounded down to the allocation granularity of 8
+static_assert(128 * 40 + 256 * 56 + 256 * 160 <= NUM_THREADS * LAUNCH_REGS, "register budgets exceed the CTA's pool");
 constexpr int CHUNK_KB = 2;  // K blocks accumulated inside the tensor cores before a partial is drained
 constexpr int TMEM_COLS = 512;
 
@@ -102,7 +106,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(raw_full(s), 1);
-      mbar_init(split_full(s), 4);
+      mbar_init(split_full(s), 8);
       mbar_init(stage_free(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -214,11 +218,11 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   }
-  } else if (warp >= 8) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
-    // ---- drain + epilogue: warps 8..15. Warp w reads TMEM lanes [32*(w%4), +32) and columns [128*h, +128) ----
+  } else if (warp >= 12) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+    // ---- drain + epilogue: warps 12..19. Warp w reads TMEM lanes [32*(w%4), +32) and columns [128*h, +128) ----
     const int quad = warp & 3;
-    const int half = (warp - 8) >> 2;
+    const int half = (warp - 12) >> 2;
     int chunk_index = 0;
     bool ok = true;
     const bool use_beta = p.beta != 0.f;
@@ -264,9 +268,9 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
-    // ---- split: warps 4..7 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
-    const int t = threadIdx.x - 4 * 32;  // 0..127
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    // ---- split: warps 4..11 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
+    const int t = threadIdx.x - 4 * 32;  // 0..255
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -279,7 +283,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES);
         float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
 #pragma unroll 4
-        for (int c = t; c < CHUNKS; c += 128) {
+        for (int c = t; c < CHUNKS; c += 256) {
           const float4 x = main_ptr[c];
           float4 hi, lo;
           hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
@@ -335,6 +339,11 @@ template <int BN, bool A_MN, bool B_MN>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid,
                            cudaStream_t stream) {
   auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN>;
+  // The kernel re-balances registers between its warpgroups; that only works while the registers the compiler gave
+  // each thread at launch cover the budgets it asks for. Refuse (the CUDA-core kernel runs instead) otherwise.
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
+  if (attr.numRegs * NUM_THREADS < 128 * 40 + 256 * 56 + 256 * 160) return cudaErrorNotSupported;
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma, mb, p);
