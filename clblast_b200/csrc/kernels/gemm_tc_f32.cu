@@ -379,39 +379,52 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   if ((d.lda % 4) || (d.ldb % 4)) return cudaErrorNotSupported;
   if (d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40)) return cudaErrorNotSupported;
 
-  constexpr int BN = 256;
+  // Tile width: 256 columns amortise the operand traffic best; 128 columns give twice as many tiles and one more
+  // pipeline stage, which wins while 256-wide tiles would leave SMs idle.
+  static int sm_counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
+  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256);
+  const int bn = tiles_wide >= 2LL * sm_counts[dev] ? 256 : 128;
+
   CUtensorMap map_a, map_b;
   if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig, BM)) return cudaErrorNotSupported;
-  if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, BN)) return cudaErrorNotSupported;
+  if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, bn)) return cudaErrorNotSupported;
 
   Tc32Params p;
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
   p.tiles_m = static_cast<int>((d.m + BM - 1) / BM);
-  p.tiles_n = static_cast<int>((d.n + BN - 1) / BN);
+  p.tiles_n = static_cast<int>((d.n + bn - 1) / bn);
   p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 16;
 
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   const int grid = static_cast<int>(tiles < sm_counts[dev] ? tiles : sm_counts[dev]);
 
-  *name = "tc_f32_3xtf32_128x256x32";
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
-  if (a_mn) {
-    return b_mn ? launch_variant<BN, true, true>(map_a, map_b, p, grid, stream)
-                : launch_variant<BN, true, false>(map_a, map_b, p, grid, stream);
+  if (bn == 256) {
+    *name = "tc_f32_3xtf32_128x256x32";
+    if (a_mn) {
+      return b_mn ? launch_variant<256, true, true>(map_a, map_b, p, grid, stream)
+                  : launch_variant<256, true, false>(map_a, map_b, p, grid, stream);
+    }
+    return b_mn ? launch_variant<256, false, true>(map_a, map_b, p, grid, stream)
+                : launch_variant<256, false, false>(map_a, map_b, p, grid, stream);
   }
-  return b_mn ? launch_variant<BN, false, true>(map_a, map_b, p, grid, stream)
-              : launch_variant<BN, false, false>(map_a, map_b, p, grid, stream);
+  *name = "tc_f32_3xtf32_128x128x32";
+  if (a_mn) {
+    return b_mn ? launch_variant<128, true, true>(map_a, map_b, p, grid, stream)
+                : launch_variant<128, true, false>(map_a, map_b, p, grid, stream);
+  }
+  return b_mn ? launch_variant<128, false, true>(map_a, map_b, p, grid, stream)
+              : launch_variant<128, false, false>(map_a, map_b, p, grid, stream);
 }
 
 }  // namespace b200
