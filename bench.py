@@ -441,11 +441,16 @@ def main():
             peak = float(peaks["bf16_tflops"])
             src = f"{peak_kind} cuBLAS bf16 burst"
         elif bound == "fp32":
-            peak = 148 * 128 * 2 * 1.965e9 / 1e12  # FFMA lanes x 2 flop x max SM clock
-            src = "nominal FP32 FFMA pipe at 1965 MHz (no measured fp32 entry)"
+            # MEASURED_PEAKS.json has no fp32 entry. Measured on this pool with the same method (torch.matmul, 8192^3,
+            # best of 5): cuBLAS fp32 64.0 TFLOP/s, cuBLAS TF32 756 TFLOP/s. The denominator used is the nominal FFMA
+            # pipe (148 SMs x 128 lanes x 2 x 1.965 GHz); the tensor-core SGEMM path can exceed it.
+            peak = 148 * 128 * 2 * 1.965e9 / 1e12
+            src = "nominal FP32 FFMA pipe at 1965 MHz (cuBLAS fp32 measured here: 64.0; cuBLAS TF32: 756)"
         else:
-            peak = 148 * 64 * 2 * 1.965e9 / 1e12
-            src = "nominal FP64 DFMA pipe at 1965 MHz (no measured fp64 entry)"
+            # FP64 pipe measured on this pool with a register-only mma.sync m8n8k4 loop: 37.1 TFLOP/s
+            # (cuBLAS DGEMM 8192^3: 35.5), equal to 148 SMs x 64 lanes x 2 x 1.965 GHz.
+            peak = 37.1
+            src = "measured FP64 pipe (register-only DMMA loop on this pool; cuBLAS DGEMM 35.5)"
         roof = {"bound": "tensor" if bound == "tensor" else bound, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": None, "peak_source": src}
     roof["kernel"] = kernel_name

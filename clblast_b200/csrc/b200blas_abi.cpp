@@ -236,7 +236,10 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_tc_f32(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);
       break;
-    case 64: err = launch_simt_f64(d, stream, &name); break;
+    case 64:
+      err = launch_dmma_f64(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_simt_f64(d, stream, &name);
+      break;
     case 16:
       err = launch_tc_f16(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f16(d, stream, &name);

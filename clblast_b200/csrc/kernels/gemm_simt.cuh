@@ -316,8 +316,13 @@ gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
   using StA = TileStager<Tr, BM, BK, NT, A_KC>;
   using StB = TileStager<Tr, BN, BK, NT, B_KC>;
 
-  __shared__ __align__(16) S sA_all[GROUPS][2][BK * LDA_S];
-  __shared__ __align__(16) S sB_all[GROUPS][2][BK * LDB_S];
+  // Dynamic shared memory (configurations above 48 KB need the opt-in attribute the launcher sets):
+  // [GROUPS][2][BK * LDA_S] for A followed by [GROUPS][2][BK * LDB_S] for B.
+  extern __shared__ __align__(16) unsigned char simt_smem[];
+  using ATiles = S[2][BK * LDA_S];
+  using BTiles = S[2][BK * LDB_S];
+  ATiles* const sA_all = reinterpret_cast<ATiles*>(simt_smem);
+  BTiles* const sB_all = reinterpret_cast<BTiles*>(simt_smem + sizeof(ATiles) * GROUPS);
 
   const int group = (GROUPS > 1) ? threadIdx.x / NT : 0;
   const int tid = (GROUPS > 1) ? threadIdx.x % NT : threadIdx.x;
@@ -483,7 +488,13 @@ struct SimtLauncher {
     const long long ctas = (p.total_tiles + GROUPS - 1) / GROUPS;
     const unsigned grid = static_cast<unsigned>(ctas < max_grid ? ctas : max_grid);
     constexpr int NT = (BM / TM) * (BN / TN) * GROUPS;
-    gemm_simt_kernel<Tr, BM, BN, BK, TM, TN, A_KC, B_KC, CONV, MINB, GROUPS><<<grid, NT, 0, stream>>>(p);
+    constexpr size_t SMEM = sizeof(S) * 2 * BK * ((BM + 4) + (BN + 4)) * GROUPS;
+    auto kernel = gemm_simt_kernel<Tr, BM, BN, BK, TM, TN, A_KC, B_KC, CONV, MINB, GROUPS>;
+    if (SMEM > 48 * 1024) {  // per-context opt-in, repeated per launch because contexts come and go
+      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+      if (e != cudaSuccess) return e;
+    }
+    kernel<<<grid, NT, SMEM, stream>>>(p);
     return cudaGetLastError();
   }
 

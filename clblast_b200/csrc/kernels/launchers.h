@@ -19,6 +19,9 @@ cudaError_t launch_simt_c64(const GemmDesc& d, cudaStream_t stream, const char**
 // the call does not meet the kernel's layout and alignment requirements; the caller then uses the CUDA-core path.
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name);
 
+// DGEMM on the FP64 tensor-core instructions (mma.sync m8n8k4). Same contract as launch_tc_f16.
+cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char** name);
+
 // Tensor-core SGEMM (error-compensated 3xTF32). Same contract as launch_tc_f16.
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 cudaError_t tc_f32_status(unsigned int out[4], bool clear);

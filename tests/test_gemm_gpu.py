@@ -49,7 +49,7 @@ def run_and_check(torch, rng, precision, layout, ta, tb, m, n, k, alpha, beta, a
     scale = (8.0 if precision > 100 else 4.0) * k * abs(alpha) + 2.0 * abs(beta) + 1e-30
     err = np.abs(H.oracle.widen(precision, got[mask]) - want[mask]).max() / scale
     assert err < TIGHT[precision], f"normalised error {err:.3e}"
-    if precision in (32, 64) and not cb.last_kernel().startswith("tc_"):
+    if precision in (32, 64) and cb.last_kernel().startswith("simt_"):
         # same order of operations as the reference kernels (k ascending, fused multiply-add, fused epilogue):
         # bit-identical to the reference-order oracle, which is itself bit-identical to the reference's kernel source
         typed = c_in.copy()
