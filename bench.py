@@ -249,9 +249,12 @@ def time_steps(torch, fn, steps, warmup, dist=None):
 
 def cpu_sample(w, seconds_target=12.0):
     """Times the oracle port on a bounded sample of the workload. Returns (tflops, cores, description)."""
+    cores = os.cpu_count() or 1
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; the CPU baseline uses every host core, so the variable is
+    # set before the OpenMP runtime inside the oracle library is loaded.
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     from oracle import cpu_oracle as oracle
     oracle.build()
-    cores = os.cpu_count() or 1
     rng = np.random.default_rng(0)
     p = w["precision"]
     dt = oracle.NP_OF[p]
@@ -324,6 +327,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--no-sweep", action="store_true", help="skip the short per-config sweep added at N=1")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sm-budget", type=int, default=-1,
+                    help="SMs the persistent GEMM kernels may use; default: all at N=1, 132 of 148 at N>1 so the "
+                         "overlapped NCCL broadcast has SMs to run on")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -351,6 +357,8 @@ def main():
     if args.gpus != world and rank == 0:
         print(f"note: --gpus {args.gpus} but WORLD_SIZE is {world}; using {world}", file=sys.stderr)
     n_gpus = world
+    sm_budget = args.sm_budget if args.sm_budget >= 0 else (132 if world > 1 and w["kind"] == "gemm" else 0)
+    cb.set_sm_budget(sm_budget)
     device = torch.device("cuda", local_rank)
     peaks, peak_kind = load_peaks()
 
@@ -405,6 +413,8 @@ def main():
     # Dominant kernel alone (no collective), CUDA events on the launching stream: the roofline numerator. Kernels
     # shorter than the host's per-call cost are replayed from a CUDA graph so that the GPU, not the Python caller,
     # sets the pace; the plain back-to-back figure is kept beside it.
+    cb.set_sm_budget(0)  # the kernel alone may use every SM
+
     def kernel_only():
         launch(cb, w, t, torch.cuda.current_stream())
     kms = time_steps(torch, kernel_only, args.steps, 3, None) / args.steps
@@ -473,6 +483,7 @@ def main():
         if sustained["peak"]:
             sustained["frac"] = sustained["value"] / float(sustained["peak"])
 
+    cb.set_sm_budget(sm_budget)
     # End to end through the host-synchronous API with pinned host buffers.
     host = {}
     h2d = d2h = 0
@@ -516,7 +527,7 @@ def main():
         "vs_baseline": None, "dtype": {16: "f16", 32: "f32", 64: "f64"}[w["precision"]], "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in w.items() if k not in ("kind", "bound")},
                    "per_gpu": "one full copy of the workload per GPU; B re-broadcast from rank 0 every step, overlapped with the previous step's GEMM" if n_gpus > 1
-                   else "single GPU", "l2": "inputs larger than L2 (no flush needed)" if min_bytes_of(w) > 126e6
+                   else "single GPU", "sm_budget": sm_budget or "all", "l2": "inputs larger than L2 (no flush needed)" if min_bytes_of(w) > 126e6
                    else "working set fits in L2; no flush between iterations"},
         "roofline": roof,
         "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -46,6 +46,8 @@ def lib() -> ctypes.CDLL:
     L.b200blas_override_parameters.argtypes = [i, c_char_p, i, POINTER(c_char_p), POINTER(sz), sz]
     L.b200blas_retrieve_parameters.restype = i
     L.b200blas_retrieve_parameters.argtypes = [i, c_char_p, i, POINTER(c_char_p), POINTER(sz), sz, POINTER(sz)]
+    L.b200blas_set_sm_budget.restype = None
+    L.b200blas_set_sm_budget.argtypes = [i]
     L.b200blas_last_kernel.restype = c_char_p
     L.b200blas_last_kernel.argtypes = []
     L.b200blas_launch_count.restype = c_uint64
@@ -61,5 +63,5 @@ C_ABI_SYMBOLS = [
     "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_gemm_batched_static",
     "b200blas_convgemm",
     "b200blas_gemm_temp_buffer_size", "b200blas_clear_cache", "b200blas_fill_cache", "b200blas_override_parameters",
-    "b200blas_retrieve_parameters", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
+    "b200blas_retrieve_parameters", "b200blas_set_sm_budget", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
 ]

@@ -243,6 +243,11 @@ def RetrieveParameters(device: int, kernel_name: str, precision):
     return _status(st), {c_names[i].decode(): c_vals[i] for i in range(n)}
 
 
+def set_sm_budget(sms: int) -> None:
+    """Limits how many SMs the persistent tensor-core kernels occupy (0 = all), e.g. to leave room for a collective."""
+    lib().b200blas_set_sm_budget(int(sms))
+
+
 def last_kernel() -> str:
     """Kernel family chosen by the most recent compute call on this thread."""
     return lib().b200blas_last_kernel().decode()

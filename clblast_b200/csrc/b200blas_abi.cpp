@@ -51,6 +51,7 @@ constexpr int kNo = 111, kYes = 112, kConjugate = 113;
 constexpr int kCrossCorrelation = 151, kConvolution = 152;
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_sm_budget{0};
 thread_local const char* t_last_kernel = "none";
 
 size_t dtype_size(int dtype) {
@@ -287,6 +288,8 @@ bool force_small_family(int dtype, size_t m, size_t n, size_t k) {
 }
 
 }  // namespace
+
+int sm_budget() { return g_sm_budget.load(std::memory_order_relaxed); }
 
 // ---- bridge for the allocation-free batched entry point ------------------------------------------------------
 // Same argument checks, normalisation and table layout as b200blas_gemm_batched above, but the tables are written
@@ -637,6 +640,8 @@ extern "C" int b200blas_gemm_temp_buffer_size(int dtype, int layout, int ta, int
   *temp_buffer_size = 0;
   return kSuccess;
 }
+
+extern "C" void b200blas_set_sm_budget(int sms) { g_sm_budget.store(sms > 0 ? sms : 0, std::memory_order_relaxed); }
 
 extern "C" int b200blas_clear_cache(void) { return kSuccess; }
 extern "C" int b200blas_fill_cache(int) { return kSuccess; }

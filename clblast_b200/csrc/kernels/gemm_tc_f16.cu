@@ -400,7 +400,9 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   const int sm_count = sm_counts[dev];
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
-  const int grid = static_cast<int>(tiles < sm_count ? tiles : sm_count);
+  int sms = sm_count;
+  if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   *name = "tc_f16_128x256x64";
   hgemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError();

@@ -404,7 +404,9 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
-  const int grid = static_cast<int>(tiles < sm_counts[dev] ? tiles : sm_counts[dev]);
+  int sms = sm_counts[dev];
+  if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
 
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
   if (bn == 256) {

@@ -34,6 +34,9 @@ cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, con
 // expired in some CTA (1 producer, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready), out[1] is the block.
 cudaError_t tc_f16_status(unsigned int out[4], bool clear);
 
+// Number of SMs persistent kernels may occupy (0 = all); set through b200blas_set_sm_budget.
+int sm_budget();
+
 // One tile configuration of the CUDA-core family as seen by the selection table.
 struct SimtConfig {
   int bm, bn;      // tile extents

@@ -91,6 +91,11 @@ int b200blas_override_parameters(int device, const char* kernel_name, int precis
 int b200blas_retrieve_parameters(int device, const char* kernel_name, int precision, const char** names,
                                  size_t* values, size_t capacity, size_t* count);
 
+/* Limits how many SMs the persistent tensor-core kernels occupy (0 = all, the default). A caller that overlaps a
+ * GEMM with a collective or a copy kernel on another stream leaves those a few SMs this way. Process-wide.
+ * No counterpart in the reference. */
+void b200blas_set_sm_budget(int sms);
+
 /* Introspection for tests and benchmarks (no counterpart in the reference). */
 
 /* Name of the kernel family the selection table picked for the most recent compute call on this thread,
