@@ -8,8 +8,9 @@
 // padded or transposed in memory. The reference accumulates half GEMMs in half; here products are exact and
 // sums are fp32, rounded to half once (alpha*acc + beta*c is evaluated in fp32).
 //
-// Operand requirements (checked on the host, otherwise the CUDA-core kernel runs): both operands K-contiguous
-// after normalisation, 16-byte aligned base addresses and leading dimensions that are multiples of 8 elements.
+// Operand requirements (checked on the host, otherwise the CUDA-core kernel runs): 16-byte aligned base addresses
+// and leading dimensions that are multiples of 8 elements. Both operand orientations are consumed where they lie
+// (K-major tiles for K-contiguous operands, MN-major column blocks otherwise); nothing is transposed in memory.
 //
 // Roles per CTA (192 threads): warp 0 lane 0 issues TMA loads; warp 1 owns TMEM and lane 0 issues the MMAs;
 // warps 2-5 drain accumulators (each warp reads the 32 TMEM lanes its rank modulo 4 may access).
@@ -124,6 +125,18 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Same for an MN-major 16-bit tile: 128-byte rows of 64 elements (one per k), leading byte offset 8192 (next
+// 64-element column block), stride byte offset 1024 (next group of eight k).
+__device__ __forceinline__ uint64_t mnmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>(8192 >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulator (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15,
 // 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
@@ -171,6 +184,9 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm
   tn = in_group / rows;
 }
 
+// A_MN / B_MN: the operand is M/N-contiguous and is loaded as 64-element-wide MN-major column blocks (one 128-byte
+// row per k) instead of one K-major tile (128-byte rows along K).
+template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -229,8 +245,20 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, tm * BM);
-          tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, tn * BN);
+          if (A_MN) {  // column blocks of 64 rows x 64 k = 8 KB each
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, &map_a, full_bar(stage), tm * BM + j * 64, kb * BK);
+          } else {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, tm * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &map_b, full_bar(stage), tn * BN + j * 64, kb * BK);
+          } else {
+            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, tn * BN);
+          }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -251,7 +279,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+      constexpr uint32_t idesc = make_idesc(BM, BN) | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -267,12 +295,15 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tcgen05_fence_after();
           const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_BYTES;
-          const uint64_t da = kmajor_sw128_desc(a_src);
-          const uint64_t db = kmajor_sw128_desc(b_src);
+          // K-major: 128-byte rows along K, advance 16 halves = 32 B per MMA. MN-major: one 128-byte row of 64
+          // elements per k, swizzle atoms of eight k (1024 B, the stride offset), column blocks 8192 B apart (the
+          // leading offset), advance 16 k = 2048 B per MMA.
+          const uint64_t da = A_MN ? mnmajor_sw128_desc(a_src) : kmajor_sw128_desc(a_src);
+          const uint64_t db = B_MN ? mnmajor_sw128_desc(b_src) : kmajor_sw128_desc(b_src);
+          constexpr uint32_t a_step = A_MN ? (2048u >> 4) : 2u, b_step = B_MN ? (2048u >> 4) : 2u;
 #pragma unroll
           for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-            // advancing K by 16 halves = 32 bytes inside the swizzle row = 2 units of the address field
-            umma_f16(d_tmem, da + 2u * ks, db + 2u * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, da + a_step * ks, db + b_step * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // frees the stage once the MMAs above have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -330,18 +361,31 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
-bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
+bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows,
+                        bool mn_contig) {
   const DriverApi& drv = driver_api();
   if (!drv.ok) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  // K-contiguous: map {K, rows}, box {64 k, box_rows}. M/N-contiguous: map {rows, K}, box {64 rows, 64 k}.
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_contig ? rows : k), static_cast<cuuint64_t>(mn_contig ? k : rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(mn_contig ? BK : box_rows)};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
                                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid,
+                           cudaStream_t stream) {
+  auto kernel = hgemm_tc_kernel<A_MN, B_MN>;
+  // per-context opt-in to more than 48 KB of dynamic shared memory, repeated per launch (contexts come and go)
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -357,7 +401,6 @@ cudaError_t tc_f16_status(unsigned int out[4], bool clear) {
 
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 16 || d.is_conv || d.batch != 1 || d.force_small) return cudaErrorNotSupported;
-  if (!d.a_kcontig || !d.b_kcontig) return cudaErrorNotSupported;
   if (d.m < 128 || d.n < 64 || d.k < 64) return cudaErrorNotSupported;
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const __half* a = static_cast<const __half*>(d.a) + d.a_off;
@@ -368,8 +411,8 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   if (d.lda * 2 >= (1LL << 40) || d.ldb * 2 >= (1LL << 40)) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
-  if (!encode_operand_map(&map_a, a, d.m, d.k, d.lda, BM)) return cudaErrorNotSupported;
-  if (!encode_operand_map(&map_b, b, d.n, d.k, d.ldb, BN)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_a, a, d.m, d.k, d.lda, BM, !d.a_kcontig)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, b, d.n, d.k, d.ldb, BN, !d.b_kcontig)) return cudaErrorNotSupported;
 
   TcParams p;
   p.c = static_cast<__half*>(d.c) + d.c_off;
@@ -392,11 +435,6 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
   if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  {
-    const cudaError_t e =
-        cudaFuncSetAttribute(hgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-  }
   const int sm_count = sm_counts[dev];
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
@@ -404,8 +442,13 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   *name = "tc_f16_128x256x64";
-  hgemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
-  return cudaGetLastError();
+  const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
+  if (a_mn) {
+    return b_mn ? launch_variant<true, true>(map_a, map_b, p, grid, stream)
+                : launch_variant<true, false>(map_a, map_b, p, grid, stream);
+  }
+  return b_mn ? launch_variant<false, true>(map_a, map_b, p, grid, stream)
+              : launch_variant<false, false>(map_a, map_b, p, grid, stream);
 }
 
 }  // namespace b200
