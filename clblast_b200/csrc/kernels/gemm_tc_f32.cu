@@ -59,6 +59,11 @@ struct Tc32Params {
   int tiles_m, tiles_n, k_blocks;
   float alpha, beta;
   int raster_group;
+  // convolution only: op(A) is gathered from the image, one GEMM per image
+  const float* image;
+  long long image_stride, c_stride;
+  int batch;
+  ConvGeom conv;
 };
 
 template <int BN>
@@ -69,6 +74,14 @@ struct Cfg {
   static constexpr int STAGES = (BN == 256) ? 2 : 3;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
+
+// Convolution tiles: m fastest, then n, then the image index.
+__device__ __forceinline__ void conv_tile_coords(const Tc32Params& p, int tile, int& tm, int& tn, int& image) {
+  tm = tile % p.tiles_m;
+  const int rest = tile / p.tiles_m;
+  tn = rest % p.tiles_n;
+  image = rest / p.tiles_n;
+}
 
 __device__ __forceinline__ void tile_coords(const Tc32Params& p, int tile, int& tm, int& tn) {
   const int per_group = p.raster_group * p.tiles_n;
@@ -81,7 +94,9 @@ __device__ __forceinline__ void tile_coords(const Tc32Params& p, int tile, int& 
 }
 
 // A_MN / B_MN: the operand is M/N-contiguous (MN-major tiles) instead of K-contiguous (K-major tiles).
-template <int BN, bool A_MN, bool B_MN>
+// CONV: op(A) is the implicit im2col matrix of one image (rows = output pixels, always MN-major); the split warps
+// gather it straight from the image into the swizzled big/small tiles, so only B (the weights) travels by TMA.
+template <int BN, bool A_MN, bool B_MN, bool CONV>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const Tc32Params p) {
@@ -104,7 +119,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * (CONV ? p.batch : 1);
+  // register budgets (split, drain): the convolution variant prefetches its gather in registers and drains 64
+  // columns per thread
+  constexpr int SPLIT_REGS = CONV ? 88 : 56;
+  constexpr int DRAIN_REGS = CONV ? 104 : 160;
+  static_assert(128 * 40 + 256 * SPLIT_REGS + 256 * DRAIN_REGS <= NUM_THREADS * LAUNCH_REGS, "register budgets");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -142,12 +162,14 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(p, tile, tm, tn);
+        int tm, tn, image_index = 0;
+        if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else tile_coords(p, tile, tm, tn);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_status)) { ok = false; break; }
-          mbar_arrive_expect_tx(raw_full(stage), C::A_BYTES + C::B_BYTES);
-          if (A_MN) {
+          mbar_arrive_expect_tx(raw_full(stage), CONV ? C::B_BYTES : C::A_BYTES + C::B_BYTES);
+          if (CONV) {
+            // op(A) is gathered by the split warps
+          } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 32; ++j)
               tma_load_2d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, kb * BK);
@@ -222,7 +244,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   }
   } else if (warp >= 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DRAIN_REGS));
     // ---- drain + epilogue: warps 12..19. Warp w reads TMEM lanes [32*(w%4), +32) and columns [128*h, +128) ----
     const int quad = warp & 3;
     const int half = (warp - 12) >> 2;
@@ -230,8 +252,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     const bool use_beta = p.beta != 0.f;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int tm, tn;
-      tile_coords(p, tile, tm, tn);
+      int tm, tn, image_index = 0;
+      if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else tile_coords(p, tile, tm, tn);
       float acc[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) acc[j] = 0.f;
@@ -259,7 +281,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
       if (row < p.m) {
-        float* cptr = p.c + static_cast<long long>(col0) * p.ldc + row;
+        float* cptr = p.c + (CONV ? image_index * p.c_stride : 0) + static_cast<long long>(col0) * p.ldc + row;
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) {
           if (col0 + j < p.n) {
@@ -271,22 +293,91 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SPLIT_REGS));
     // ---- split: warps 4..11 turn the raw fp32 tiles into TF32 big parts (in place) and small parts ----
     const int t = threadIdx.x - 4 * 32;  // 0..255
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;  // A and B main tiles are adjacent, so are the lo tiles
+    // GEMM: A and B main tiles are adjacent, so are the lo tiles, and all are split. Convolution: only B is split
+    // from its raw copy; A is produced below.
+    constexpr int CHUNK_FIRST = CONV ? C::A_BYTES / 16 : 0;
+    constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;
+    // Convolution gather: this thread owns pixel group `pg` (8 consecutive output pixels = one 32-byte swizzle chunk)
+    // of the 128-pixel tile and K rows `kr` and `kr + 16` of every K block.
+    const int pg = t & 15, kr = t >> 4;
+    float gathered[CONV ? 2 : 1][CONV ? 8 : 1];
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm = 0, tn = 0, image_index = 0;
+      const float* image = nullptr;
+      int ho0 = 0, wo0 = 0, pixels_left = 0;
+      const int khw = CONV ? p.conv.kernel_h * p.conv.kernel_w : 1;
+      if (CONV) {
+        conv_tile_coords(p, tile, tm, tn, image_index);
+        image = p.image + image_index * p.image_stride;
+        const int p_first = tm * BM + pg * 8;
+        ho0 = p_first / p.conv.out_w;
+        wo0 = p_first - ho0 * p.conv.out_w;
+        pixels_left = p.m - p_first;  // <= 0: the whole group lies beyond the image
+      }
+      auto gather = [&](int kb) {
+        if constexpr (CONV) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kg = kb * BK + kr + 16 * u;
+            const int c_id = kg / khw;
+            const int k2 = kg - c_id * khw;
+            int kh_id = k2 / p.conv.kernel_w;
+            int kw_id = k2 - kh_id * p.conv.kernel_w;
+            if (p.conv.flip) {
+              kh_id = p.conv.kernel_h - 1 - kh_id;
+              kw_id = p.conv.kernel_w - 1 - kw_id;
+            }
+            const float* plane = image + static_cast<long long>(c_id) * p.conv.height * p.conv.width;
+            const int dh = kh_id * p.conv.dil_h - p.conv.pad_h, dw = kw_id * p.conv.dil_w - p.conv.pad_w;
+            int ho = ho0, wo = wo0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int hi = ho * p.conv.stride_h + dh, wi = wo * p.conv.stride_w + dw;
+              float v = 0.f;
+              if (kg < p.k && e < pixels_left && hi >= 0 && hi < p.conv.height && wi >= 0 && wi < p.conv.width)
+                v = plane[hi * p.conv.width + wi];
+              gathered[u][e] = v;
+              if (++wo == p.conv.out_w) { wo = 0; ++ho; }
+            }
+          }
+        }
+      };
+      if (CONV) gather(0);
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES);
         float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+        if constexpr (CONV) {
+          // MN-major A tile with the 32-byte-chunk swizzle: column block pg/4 (4096 B each), row k (128 B), chunk
+          // (pg % 4) ^ (k % 4) of 32 B holding this thread's eight pixels.
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int k = kr + 16 * u;
+            const int f4 = ((pg >> 2) * 4096 + k * 128 + (((pg & 3) ^ (k & 3)) << 5)) >> 4;
+            float4 hi0, hi1, lo0, lo1;
+            hi0.x = to_tf32(gathered[u][0]); hi0.y = to_tf32(gathered[u][1]);
+            hi0.z = to_tf32(gathered[u][2]); hi0.w = to_tf32(gathered[u][3]);
+            hi1.x = to_tf32(gathered[u][4]); hi1.y = to_tf32(gathered[u][5]);
+            hi1.z = to_tf32(gathered[u][6]); hi1.w = to_tf32(gathered[u][7]);
+            lo0.x = to_tf32(gathered[u][0] - hi0.x); lo0.y = to_tf32(gathered[u][1] - hi0.y);
+            lo0.z = to_tf32(gathered[u][2] - hi0.z); lo0.w = to_tf32(gathered[u][3] - hi0.w);
+            lo1.x = to_tf32(gathered[u][4] - hi1.x); lo1.y = to_tf32(gathered[u][5] - hi1.y);
+            lo1.z = to_tf32(gathered[u][6] - hi1.z); lo1.w = to_tf32(gathered[u][7] - hi1.w);
+            main_ptr[f4] = hi0; main_ptr[f4 + 1] = hi1;
+            lo_ptr[f4] = lo0; lo_ptr[f4 + 1] = lo1;
+          }
+          if (kb + 1 < p.k_blocks) gather(kb + 1);  // in flight while B is split and the MMAs run
+        }
 #pragma unroll 4
-        for (int c = t; c < CHUNKS; c += 256) {
+        for (int c = CHUNK_FIRST + t; c < CHUNKS; c += 256) {
           const float4 x = main_ptr[c];
           float4 hi, lo;
           hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
@@ -333,15 +424,15 @@ bool encode_map(CUtensorMap* map, const void* base, long long rows, long long k,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool CONV = false>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid,
                            cudaStream_t stream) {
-  auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN>;
+  auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN, CONV>;
   // The kernel re-balances registers between its warpgroups; that only works while the registers the compiler gave
   // each thread at launch cover the budgets it asks for. Refuse (the CUDA-core kernel runs instead) otherwise.
   cudaFuncAttributes attr;
   if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
-  if (attr.numRegs * NUM_THREADS < 128 * 40 + 256 * 56 + 256 * 160) return cudaErrorNotSupported;
+  if (attr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma, mb, p);
@@ -425,6 +516,52 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   }
   return b_mn ? launch_variant<128, false, true>(map_a, map_b, p, grid, stream)
               : launch_variant<128, false, false>(map_a, map_b, p, grid, stream);
+}
+
+cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
+  if (d.dtype != 32 || !d.is_conv) return cudaErrorNotSupported;
+  static const bool forced_ffma = [] {
+    const char* v = std::getenv("B200BLAS_SGEMM");
+    return v != nullptr && std::strcmp(v, "ffma") == 0;
+  }();
+  if (forced_ffma) return cudaErrorNotSupported;
+  // weights [Cout][K] are the K-major B operand of the TMA path: 16-byte aligned rows
+  const float* weights = static_cast<const float*>(d.b) + d.b_off;
+  if ((reinterpret_cast<uintptr_t>(weights) & 15) || (d.ldb % 4)) return cudaErrorNotSupported;
+  if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF || d.batch > 0x7FFFFFFF) return cudaErrorNotSupported;
+  constexpr int BN = 128;
+  const long long tiles = ((d.m + BM - 1) / BM) * ((d.n + BN - 1) / BN) * d.batch;
+  if (d.m < 128 || d.n < 32 || d.k < 64 || tiles < 64 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+
+  CUtensorMap map_b;
+  if (!encode_map(&map_b, weights, d.n, d.k, d.ldb, false, BN)) return cudaErrorNotSupported;
+
+  Tc32Params p = {};
+  p.c = static_cast<float*>(d.c) + d.c_off;
+  p.ldc = d.ldc;
+  p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
+  p.tiles_m = static_cast<int>((d.m + BM - 1) / BM);
+  p.tiles_n = static_cast<int>((d.n + BN - 1) / BN);
+  p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
+  p.alpha = 1.f;
+  p.beta = 0.f;
+  p.raster_group = 16;
+  p.image = static_cast<const float*>(d.a) + d.a_off;
+  p.image_stride = d.a_stride;
+  p.c_stride = d.c_stride;
+  p.batch = static_cast<int>(d.batch);
+  p.conv = d.conv;
+
+  static int sm_counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
+  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  int sms = sm_counts[dev];
+  if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  *name = "tc_conv_f32_3xtf32_128x128x32";
+  return launch_variant<BN, true, false, true>(map_b, map_b, p, grid, stream);
 }
 
 }  // namespace b200

@@ -25,6 +25,8 @@ cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char**
 // Tensor-core SGEMM (error-compensated 3xTF32). Same contract as launch_tc_f16.
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 cudaError_t tc_f32_status(unsigned int out[4], bool clear);
+// Tensor-core Convgemm (same kernel, op(A) gathered from the image by the split warps).
+cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 
 // Streaming kernel for large batches of small fp32 problems (cp.async double buffering across the batch). Returns
 // cudaErrorNotSupported without launching when the call does not meet its shape and alignment requirements.
