@@ -17,7 +17,9 @@
 // ever happens. Non-finite inputs: an infinite operand yields a non-finite result in every output it touches, but
 // it may be NaN where plain fp32 arithmetic gives +-inf (inf times a negative small part); the reference's own
 // comparison rule treats the two alike (test/correctness/tester.cpp:569-577).
-// Requirements (host-checked): 16-byte aligned bases, leading dimensions multiples of 4 elements.
+// Operands whose base is 16-byte aligned and whose leading dimension is a multiple of 4 elements travel by TMA;
+// any other operand pair is gathered by the split warps with coalesced scalar loads (bounds-checked, so every
+// offset and leading dimension is accepted) and written straight into the swizzled big/small tiles.
 //
 // Roles (640 threads, five warpgroups with re-balanced register budgets): warp 0 TMA producer, warp 1 MMA issuer
 // and TMEM owner (warps 2-3 idle), warps 4-11 split, warps 12-19 drain + epilogue.
@@ -59,6 +61,10 @@ struct Tc32Params {
   int tiles_m, tiles_n, k_blocks;
   float alpha, beta;
   int raster_group;
+  // gathered operands (no TMA): element pointers and leading dimensions
+  const float* a;
+  const float* b;
+  long long lda, ldb;
   // convolution only: op(A) is gathered from the image, one GEMM per image
   const float* image;
   long long image_stride, c_stride;
@@ -94,14 +100,19 @@ __device__ __forceinline__ void tile_coords(const Tc32Params& p, int tile, int& 
 }
 
 // A_MN / B_MN: the operand is M/N-contiguous (MN-major tiles) instead of K-contiguous (K-major tiles).
-// CONV: op(A) is the implicit im2col matrix of one image (rows = output pixels, always MN-major); the split warps
-// gather it straight from the image into the swizzled big/small tiles, so only B (the weights) travels by TMA.
-template <int BN, bool A_MN, bool B_MN, bool CONV>
+// MODE kConv: op(A) is the implicit im2col matrix of one image (rows = output pixels, always MN-major); the split
+// warps gather it straight from the image into the swizzled big/small tiles, so only B (the weights) travels by TMA.
+// MODE kGather: both operands are gathered by the split warps; the TMA warp only forwards "stage free".
+constexpr int kTma = 0, kConv = 1, kGather = 2;
+template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const Tc32Params p) {
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES;
+  constexpr bool CONV = MODE == kConv;
+  constexpr bool GATHER = MODE == kGather;
+  static_assert(!GATHER || BN == 128, "the gathered variant prefetches 16 + 16 values per thread");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
@@ -122,8 +133,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int num_tiles = p.tiles_m * p.tiles_n * (CONV ? p.batch : 1);
   // register budgets (split, drain): the convolution variant prefetches its gather in registers and drains 64
   // columns per thread
-  constexpr int SPLIT_REGS = CONV ? 88 : 56;
-  constexpr int DRAIN_REGS = CONV ? 104 : 160;
+  constexpr int SPLIT_REGS = (CONV || GATHER) ? 88 : 56;
+  constexpr int DRAIN_REGS = (CONV || GATHER) ? 104 : 160;
   static_assert(128 * 40 + 256 * SPLIT_REGS + 256 * DRAIN_REGS <= NUM_THREADS * LAUNCH_REGS, "register budgets");
 
   if (threadIdx.x == 0) {
@@ -166,6 +177,11 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else tile_coords(p, tile, tm, tn);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_status)) { ok = false; break; }
+          if (GATHER) {
+            mbar_arrive(raw_full(stage));  // nothing to load: tell the split warps the stage is theirs
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_arrive_expect_tx(raw_full(stage), CONV ? C::B_BYTES : C::A_BYTES + C::B_BYTES);
           if (CONV) {
             // op(A) is gathered by the split warps
@@ -301,12 +317,16 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     // GEMM: A and B main tiles are adjacent, so are the lo tiles, and all are split. Convolution: only B is split
     // from its raw copy; A is produced below.
-    constexpr int CHUNK_FIRST = CONV ? C::A_BYTES / 16 : 0;
     constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;
+    constexpr int CHUNK_FIRST = GATHER ? CHUNKS : CONV ? C::A_BYTES / 16 : 0;
     // Convolution gather: this thread owns pixel group `pg` (8 consecutive output pixels = one 32-byte swizzle chunk)
     // of the 128-pixel tile and K rows `kr` and `kr + 16` of every K block.
     const int pg = t & 15, kr = t >> 4;
     float gathered[CONV ? 2 : 1][CONV ? 8 : 1];
+    // Plain gather: warp `sw` of the eight split warps, lane = position along the contiguous direction, so every
+    // load instruction reads one 128-byte run. Sixteen values per operand and K block are held in registers.
+    const int sw = t >> 5;
+    float ga[GATHER ? 16 : 1], gb[GATHER ? 16 : 1];
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm = 0, tn = 0, image_index = 0;
       const float* image = nullptr;
@@ -348,7 +368,54 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       };
+      if (GATHER) tile_coords(p, tile, tm, tn);
+      // One operand tile of 128 rows x 32 k. MN-contiguous: value j sits at k = sw + 8 (j / 4), row 32 (j % 4) + lane.
+      // K-contiguous: value j sits at row sw + 8 j, k = lane.
+      auto gather_plain = [&](float (&v)[GATHER ? 16 : 1], const float* src, long long ld, bool mn_major, int row0,
+                              int rows_total, int kb) {
+        if constexpr (GATHER) {
+          if (mn_major) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int kg = kb * BK + sw + 8 * (j >> 2);
+              const int row = row0 + 32 * (j & 3) + lane;
+              v[j] = (kg < p.k && row < rows_total) ? src[static_cast<long long>(kg) * ld + row] : 0.f;
+            }
+          } else {
+            const int kg = kb * BK + lane;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int row = row0 + sw + 8 * j;
+              v[j] = (kg < p.k && row < rows_total) ? src[static_cast<long long>(row) * ld + kg] : 0.f;
+            }
+          }
+        }
+      };
+      // Writes the sixteen values as TF32 big / small parts at their swizzled positions (conflict-free: the 32 lanes
+      // of a warp fill one 128-byte row).
+      auto store_plain = [&](const float (&v)[GATHER ? 16 : 1], uint8_t* main_tile, uint8_t* lo_tile, bool mn_major) {
+        if constexpr (GATHER) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            int off;
+            if (mn_major) {
+              const int k = sw + 8 * (j >> 2);
+              off = (j & 3) * 4096 + k * 128 + ((((lane >> 3) ^ (k & 3))) << 5) + (lane & 7) * 4;
+            } else {
+              const int row = sw + 8 * j;
+              off = row * 128 + (((lane >> 2) ^ (row & 7)) << 4) + (lane & 3) * 4;
+            }
+            const float hi = to_tf32(v[j]);
+            *reinterpret_cast<float*>(main_tile + off) = hi;
+            *reinterpret_cast<float*>(lo_tile + off) = to_tf32(v[j] - hi);
+          }
+        }
+      };
       if (CONV) gather(0);
+      if (GATHER) {
+        gather_plain(ga, p.a, p.lda, A_MN, tm * BM, p.m, 0);
+        gather_plain(gb, p.b, p.ldb, B_MN, tn * BN, p.n, 0);
+      }
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_status);
         ok = __all_sync(0xffffffffu, ok);
@@ -375,6 +442,15 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             lo_ptr[f4] = lo0; lo_ptr[f4 + 1] = lo1;
           }
           if (kb + 1 < p.k_blocks) gather(kb + 1);  // in flight while B is split and the MMAs run
+        }
+        if constexpr (GATHER) {
+          uint8_t* const stage_ptr = base_ptr + stage * C::STAGE_BYTES;
+          store_plain(ga, stage_ptr, stage_ptr + C::A_BYTES + C::B_BYTES, A_MN);
+          store_plain(gb, stage_ptr + C::A_BYTES, stage_ptr + 2 * C::A_BYTES + C::B_BYTES, B_MN);
+          if (kb + 1 < p.k_blocks) {  // in flight while the tensor cores work on this stage
+            gather_plain(ga, p.a, p.lda, A_MN, tm * BM, p.m, kb + 1);
+            gather_plain(gb, p.b, p.ldb, B_MN, tn * BN, p.n, kb + 1);
+          }
         }
 #pragma unroll 4
         for (int c = CHUNK_FIRST + t; c < CHUNKS; c += 256) {
@@ -424,10 +500,10 @@ bool encode_map(CUtensorMap* map, const void* base, long long rows, long long k,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool CONV = false>
+template <int BN, bool A_MN, bool B_MN, int MODE = kTma>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid,
                            cudaStream_t stream) {
-  auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN, CONV>;
+  auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN, MODE>;
   // The kernel re-balances registers between its warpgroups; that only works while the registers the compiler gave
   // each thread at launch cover the budgets it asks for. Refuse (the CUDA-core kernel runs instead) otherwise.
   cudaFuncAttributes attr;
@@ -464,9 +540,9 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
-  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
-  if ((d.lda % 4) || (d.ldb % 4)) return cudaErrorNotSupported;
-  if (d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40)) return cudaErrorNotSupported;
+  // TMA needs 16-byte aligned rows; everything else is gathered with plain loads by the split warps.
+  const bool gathered = (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
+                        (d.lda % 4) || (d.ldb % 4) || d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40);
 
   // Tile width: 256 columns amortise the operand traffic best; 128 columns give twice as many tiles and one more
   // pipeline stage, which wins while 256-wide tiles would leave SMs idle.
@@ -476,13 +552,20 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
   if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
   const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256);
-  const int bn = tiles_wide >= 2LL * sm_counts[dev] ? 256 : 128;
+  const int bn = (!gathered && tiles_wide >= 2LL * sm_counts[dev]) ? 256 : 128;
 
   CUtensorMap map_a, map_b;
-  if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig, BM)) return cudaErrorNotSupported;
-  if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, bn)) return cudaErrorNotSupported;
+  if (gathered) {
+    std::memset(&map_a, 0, sizeof(map_a));
+    std::memset(&map_b, 0, sizeof(map_b));
+  } else {
+    if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig, BM)) return cudaErrorNotSupported;
+    if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, bn)) return cudaErrorNotSupported;
+  }
 
-  Tc32Params p;
+  Tc32Params p = {};
+  p.a = a; p.b = b;
+  p.lda = d.lda; p.ldb = d.ldb;
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
@@ -500,6 +583,15 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
 
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
+  if (gathered) {
+    *name = "tc_f32_3xtf32_gather_128x128x32";
+    if (a_mn) {
+      return b_mn ? launch_variant<128, true, true, kGather>(map_a, map_b, p, grid, stream)
+                  : launch_variant<128, true, false, kGather>(map_a, map_b, p, grid, stream);
+    }
+    return b_mn ? launch_variant<128, false, true, kGather>(map_a, map_b, p, grid, stream)
+                : launch_variant<128, false, false, kGather>(map_a, map_b, p, grid, stream);
+  }
   if (bn == 256) {
     *name = "tc_f32_3xtf32_128x256x32";
     if (a_mn) {
@@ -561,7 +653,7 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   *name = "tc_conv_f32_3xtf32_128x128x32";
-  return launch_variant<BN, true, false, true>(map_b, map_b, p, grid, stream);
+  return launch_variant<BN, true, false, kConv>(map_b, map_b, p, grid, stream);
 }
 
 }  // namespace b200

@@ -54,11 +54,58 @@ def test_ragged_edges_k_tail_offsets(cuda, layout, ta, tb):
     run_tc32(cuda, rng, layout, ta, tb, 700, 900, 300, -0.5, 0.0, pad=(12, 0, 5))
 
 
-def test_unaligned_or_small_problems_keep_the_cuda_core_kernel(cuda):
+def test_small_problems_keep_the_cuda_core_kernel(cuda):
     rng = np.random.default_rng(3)
-    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 600, 600, 600, 1.0, 0.0, pad=(1, 0, 0), expect_tc=False)   # lda % 4 != 0
-    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 600, 600, 600, 1.0, 0.0, offs=(2, 0, 0), expect_tc=False)  # base not 16 B
-    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 200, 200, 200, 1.0, 0.0, expect_tc=False)                  # too small
+    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 200, 200, 200, 1.0, 0.0, expect_tc=False)
+    run_tc32(cuda, rng, H.COL, H.NO, H.NO, 200, 200, 200, 1.0, 0.0, pad=(1, 0, 0), expect_tc=False)
+
+
+@pytest.mark.parametrize("layout,ta,tb", ALL)
+def test_unaligned_operands_are_gathered_on_the_tensor_cores(cuda, layout, ta, tb):
+    """Leading dimensions that are not multiples of four elements, or bases off the 16-byte grid, cannot travel by
+    TMA: the split warps load such operands with bounds-checked scalar loads instead. Every orientation, odd
+    leading dimensions, odd offsets, ragged M / N / K."""
+    rng = np.random.default_rng(4)
+    run_tc32(cuda, rng, layout, ta, tb, 600, 600, 600, 1.0, 0.0, pad=(1, 0, 0))     # lda % 4 != 0
+    assert cb.last_kernel().startswith("tc_f32_3xtf32_gather")
+    run_tc32(cuda, rng, layout, ta, tb, 600, 600, 600, 1.0, 0.0, offs=(2, 0, 0))    # base of A not 16-byte aligned
+    assert cb.last_kernel().startswith("tc_f32_3xtf32_gather")
+    run_tc32(cuda, rng, layout, ta, tb, 1001, 777, 515, -1.25, 0.75, offs=(3, 5, 7), pad=(3, 1, 2))
+    assert cb.last_kernel().startswith("tc_f32_3xtf32_gather")
+    run_tc32(cuda, rng, layout, ta, tb, 513, 1025, 300, 1.0, 0.0, offs=(0, 1, 0), pad=(0, 0, 0))
+    assert cb.last_kernel().startswith("tc_f32_3xtf32_gather")
+
+
+def test_config2_ragged_shape(cuda):
+    """4097 x 3071 x 1025 with leading dimensions 16 past the extents: sampled against the fp64 oracle."""
+    torch = cuda
+    m, n, k = 4097, 3071, 1025
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rs = np.random.default_rng(5)
+    for ta, tb in itertools.product((H.NO, H.YES), repeat=2):
+        a_rows, a_cols = (m, k) if ta == H.NO else (k, m)
+        b_rows, b_cols = (k, n) if tb == H.NO else (n, k)
+        lda, ldb, ldc = a_rows + 16, b_rows + 16, m + 16
+        a = torch.rand(lda * a_cols, generator=g, device="cuda") * 2 - 1
+        b = torch.rand(ldb * b_cols, generator=g, device="cuda") * 2 - 1
+        c0 = torch.rand(ldc * n, generator=g, device="cuda") * 2 - 1
+        c = c0.clone()
+        torch.cuda.synchronize()
+        assert cb.Gemm(H.COL, ta, tb, m, n, k, 1.5, a, 0, lda, b, 0, ldb, 0.5, c, 0, ldc) == 0
+        assert cb.last_kernel().startswith("tc_f32"), cb.last_kernel()
+        rows, cols = rs.integers(0, m, 2048), rs.integers(0, n, 2048)
+        rows[:4], cols[:4] = (0, m - 1, 0, m - 1), (0, 0, n - 1, n - 1)
+        ah, bh = a.cpu().numpy().astype(np.float64), b.cpu().numpy().astype(np.float64)
+        # column-major storage read as [column][row]: op(A) as [m][k], op(B) as [n][k]
+        opa = ah.reshape(a_cols, lda)[:, :a_rows]
+        opa = opa.T if ta == H.NO else opa
+        opb = bh.reshape(b_cols, ldb)[:, :b_rows]
+        opb = opb if tb == H.NO else opb.T
+        want = 1.5 * np.einsum("ik,ik->i", opa[rows], opb[cols]) + 0.5 * c0.cpu().numpy()[cols * ldc + rows]
+        mag = 1.5 * np.einsum("ik,ik->i", np.abs(opa[rows]), np.abs(opb[cols])) + 0.5
+        got = c.cpu().numpy()[cols * ldc + rows].astype(np.float64)
+        assert (np.abs(got - want) / mag).max() < 2.0 ** -20
+        assert torch.equal(c.view(n, ldc)[:, m:], c0.view(n, ldc)[:, m:])
 
 
 def test_infinite_inputs_stay_confined_to_their_outputs(cuda):
