@@ -242,7 +242,8 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_simt_f64(d, stream, &name);
       break;
     case 16:
-      err = launch_tc_f16(d, stream, &name);
+      err = launch_tc_f16_pair(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_tc_f16(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f16(d, stream, &name);
       break;
     case 3232: err = launch_simt_c32(d, stream, &name); break;
@@ -271,7 +272,10 @@ int run(const GemmDesc& d, void* stream, int async) {
     // The tensor-core kernel reports expired waits through a status word instead of hanging or trapping.
     unsigned int status[4] = {0, 0, 0, 0};
     const bool is_f32 = std::strncmp(t_last_kernel, "tc_f32", 6) == 0 || std::strncmp(t_last_kernel, "tc_conv", 7) == 0;
-    const cudaError_t serr = is_f32 ? tc_f32_status(status, true) : tc_f16_status(status, true);
+    const bool is_pair = std::strncmp(t_last_kernel, "tc_f16_pair", 11) == 0;
+    const cudaError_t serr = is_f32    ? tc_f32_status(status, true)
+                             : is_pair ? tc_f16_pair_status(status, true)
+                                       : tc_f16_status(status, true);
     if (serr == cudaSuccess && status[0] != 0) {
       std::fprintf(stderr, "b200blas: tensor-core kernel gave up waiting (code %u, block %u)\n", status[0], status[1]);
       return kUnexpectedError;

@@ -21,7 +21,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include <cstdlib>
 
 #include "../driver_api.h"
 #include "launchers.h"
@@ -426,7 +425,6 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 16;
-  if (const char* rg = std::getenv("B200BLAS_RASTER")) p.raster_group = std::atoi(rg) > 0 ? std::atoi(rg) : 16;
 
   // SM count is cached per device; the opt-in to more than 48 KB of dynamic shared memory is per context, and
   // contexts come and go, so it is simply repeated before every launch (a host-side attribute write).

@@ -18,6 +18,9 @@ cudaError_t launch_simt_c64(const GemmDesc& d, cudaStream_t stream, const char**
 // Tensor-core HGEMM (TMA + tcgen05 + TMEM). Returns cudaErrorNotSupported, without launching anything, when
 // the call does not meet the kernel's layout and alignment requirements; the caller then uses the CUDA-core path.
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name);
+// The same on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles shared by two SMs), tried first.
+cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const char** name);
+cudaError_t tc_f16_pair_status(unsigned int out[4], bool clear);
 
 // DGEMM on the FP64 tensor-core instructions (mma.sync m8n8k4). Same contract as launch_tc_f16.
 cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char** name);

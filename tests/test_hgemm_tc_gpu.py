@@ -70,6 +70,25 @@ def test_many_tiles_per_cta_exercises_both_accumulators_and_the_ring(cuda):
     run_tc(cuda, rng, H.ROW, H.NO, H.YES, 3072, 4096, 512, 1.0, 0.0)
 
 
+@pytest.mark.parametrize("layout,ta,tb", TC_LAYOUTS)
+def test_cta_pair_kernel_and_single_cta_kernel_share_the_work(cuda, layout, ta, tb):
+    """Problems with at least 256 rows (after layout normalisation) run on CTA pairs (two SMs per 256 x 256 tile);
+    narrower ones, and small ones whose last pair tile would be half empty, keep one CTA per 128 x 256 tile."""
+    rng = np.random.default_rng(6)
+    swap = layout == H.ROW  # row-major problems are computed as the transposed column-major problem
+    run_tc(cuda, rng, layout, ta, tb, *((136, 200) if swap else (200, 136)), 328, 1.0, 0.0)
+    assert cb.last_kernel() == "tc_f16_128x256x64"
+    run_tc(cuda, rng, layout, ta, tb, *((400, 336) if swap else (336, 400)), 328, 1.0, 0.5)
+    assert cb.last_kernel() == "tc_f16_128x256x64"
+    # ragged pair tiles: the second CTA of the last pair row holds 8 valid rows, the last column tile 72 columns
+    run_tc(cuda, rng, layout, ta, tb, *((2120, 2184) if swap else (2184, 2120)), 520, -1.5, 0.5, offs=(8, 16, 3),
+           pad=(8, 0, 5))
+    assert cb.last_kernel() == "tc_f16_pair_256x256x64"
+    # more tiles than CTA pairs: every pair walks several tiles, both accumulators and the whole ring are reused
+    run_tc(cuda, rng, layout, ta, tb, 3072, 4096, 200, 1.0, 0.0)
+    assert cb.last_kernel() == "tc_f16_pair_256x256x64"
+
+
 def test_unaligned_operands_fall_back_to_the_cuda_core_kernel(cuda):
     rng = np.random.default_rng(5)
     run_tc(cuda, rng, H.ROW, H.NO, H.YES, 256, 256, 128, 1.0, 0.0, pad=(1, 0, 0), expect_tc=False)   # lda % 8 != 0
