@@ -234,6 +234,7 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   switch (d.dtype) {
     case 32:
       err = d.is_conv ? launch_tc_conv_f32(d, stream, &name) : launch_small_batched_f32(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_tc_f32_pair(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_tc_f32(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);
       break;
@@ -273,9 +274,11 @@ int run(const GemmDesc& d, void* stream, int async) {
     unsigned int status[4] = {0, 0, 0, 0};
     const bool is_f32 = std::strncmp(t_last_kernel, "tc_f32", 6) == 0 || std::strncmp(t_last_kernel, "tc_conv", 7) == 0;
     const bool is_pair = std::strncmp(t_last_kernel, "tc_f16_pair", 11) == 0;
-    const cudaError_t serr = is_f32    ? tc_f32_status(status, true)
-                             : is_pair ? tc_f16_pair_status(status, true)
-                                       : tc_f16_status(status, true);
+    const bool is_f32_pair = std::strncmp(t_last_kernel, "tc_f32_3xtf32_pair", 18) == 0;
+    const cudaError_t serr = is_f32_pair ? tc_f32_pair_status(status, true)
+                             : is_f32    ? tc_f32_status(status, true)
+                             : is_pair   ? tc_f16_pair_status(status, true)
+                                         : tc_f16_status(status, true);
     if (serr == cudaSuccess && status[0] != 0) {
       std::fprintf(stderr, "b200blas: tensor-core kernel gave up waiting (code %u, block %u)\n", status[0], status[1]);
       return kUnexpectedError;

@@ -28,6 +28,9 @@ cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char**
 // Tensor-core SGEMM (error-compensated 3xTF32). Same contract as launch_tc_f16.
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 cudaError_t tc_f32_status(unsigned int out[4], bool clear);
+// The same on CTA pairs (256 x 256 tiles shared by two SMs), tried first for large problems.
+cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name);
+cudaError_t tc_f32_pair_status(unsigned int out[4], bool clear);
 // Tensor-core Convgemm (same kernel, op(A) gathered from the image by the split warps).
 cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 

@@ -54,6 +54,15 @@ def test_ragged_edges_k_tail_offsets(cuda, layout, ta, tb):
     run_tc32(cuda, rng, layout, ta, tb, 700, 900, 300, -0.5, 0.0, pad=(12, 0, 5))
 
 
+@pytest.mark.parametrize("layout,ta,tb", ALL)
+def test_cta_pair_kernel_ragged(cuda, layout, ta, tb):
+    """At least 148 tiles of 256 x 256: two SMs share a tile (cta_group::2). Ragged M / N / K, offsets, padded leading
+    dimensions, alpha and beta."""
+    rng = np.random.default_rng(7)
+    run_tc32(cuda, rng, layout, ta, tb, 3080, 3332, 168, 1.5, 0.5, offs=(4, 8, 3), pad=(4, 8, 1))
+    assert cb.last_kernel() == "tc_f32_3xtf32_pair_256x256x32"
+
+
 def test_small_problems_keep_the_cuda_core_kernel(cuda):
     rng = np.random.default_rng(3)
     run_tc32(cuda, rng, H.COL, H.NO, H.NO, 200, 200, 200, 1.0, 0.0, expect_tc=False)
