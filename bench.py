@@ -456,6 +456,11 @@ def main():
             # pipe (148 SMs x 128 lanes x 2 x 1.965 GHz); the tensor-core SGEMM path can exceed it.
             peak = 148 * 128 * 2 * 1.965e9 / 1e12
             src = "nominal FP32 FFMA pipe at 1965 MHz (cuBLAS fp32 measured here: 64.0; cuBLAS TF32: 756)"
+            if kernel_name.startswith("tc_"):
+                # error-compensated 3xTF32: three tensor-core products per fp32 product
+                bound = "tensor"
+                peak = 756.0 / 3
+                src = "cuBLAS TF32 measured on this pool (756 TFLOP/s) / 3 tensor-core products per fp32 product"
         else:
             # FP64 pipe measured on this pool with a register-only mma.sync m8n8k4 loop: 37.1 TFLOP/s
             # (cuBLAS DGEMM 8192^3: 35.5), equal to 148 SMs x 64 lanes x 2 x 1.965 GHz.
