@@ -256,6 +256,8 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   return err;
 }
 
+int tensor_core_status(int async);
+
 // Runs `d` either synchronously on the private stream or asynchronously on the caller's stream.
 int run(const GemmDesc& d, void* stream, int async) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -269,8 +271,13 @@ int run(const GemmDesc& d, void* stream, int async) {
     std::fprintf(stderr, "b200blas: CUDA error %d (%s)\n", static_cast<int>(err), cudaGetErrorString(err));
     return static_cast<int>(err);
   }
+  return tensor_core_status(async);
+}
+
+// After a synchronous call that ran a tensor-core kernel: the kernel reports expired waits through a status word
+// instead of hanging or trapping.
+int tensor_core_status(int async) {
   if (!async && std::strncmp(t_last_kernel, "tc_", 3) == 0) {
-    // The tensor-core kernel reports expired waits through a status word instead of hanging or trapping.
     unsigned int status[4] = {0, 0, 0, 0};
     const bool is_f32 = std::strncmp(t_last_kernel, "tc_f32", 6) == 0 || std::strncmp(t_last_kernel, "tc_conv", 7) == 0;
     const bool is_pair = std::strncmp(t_last_kernel, "tc_f16_pair", 11) == 0;
@@ -374,6 +381,21 @@ int prepare_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, s
     }
   }
   d.tables_aligned4 = offsets_aligned ? 1 : 0;
+  // Evenly spaced offsets (the common case) are also described by a first offset and a stride, which lets the
+  // TMA-based kernels address the batch through one tensor map.
+  const long long sa = batch_count > 1 ? h_a[1] - h_a[0] : 0;
+  const long long sb = batch_count > 1 ? h_b[1] - h_b[0] : 0;
+  const long long sc = batch_count > 1 ? h_c[1] - h_c[0] : 1;
+  bool uniform = sa >= 0 && sb >= 0 && sc > 0;
+  for (size_t i = 1; uniform && i < batch_count; ++i) {
+    const long long step = static_cast<long long>(i);
+    uniform = h_a[i] == h_a[0] + step * sa && h_b[i] == h_b[0] + step * sb && h_c[i] == h_c[0] + step * sc;
+  }
+  if (uniform) {
+    d.uniform_strides = 1;
+    d.a_off = h_a[0]; d.b_off = h_b[0]; d.c_off = h_c[0];
+    d.a_stride = sa; d.b_stride = sb; d.c_stride = sc;
+  }
   *out = d;
   return kSuccess;
 }
@@ -467,76 +489,15 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
                                      const void* b, const size_t* b_offsets, size_t b_ld, const void* betas, void* c,
                                      const size_t* c_offsets, size_t c_ld, size_t batch_count, void* stream,
                                      int async) {
-  const size_t elem = dtype_size(dtype);
-  if (elem == 0 || !valid_enums(layout, ta, tb)) return kUnexpectedError;
-  if (batch_count < 1 || !alphas || !betas || !a_offsets || !b_offsets || !c_offsets) return kInvalidBatchCount;
-  if (m == 0 || n == 0 || k == 0) return kInvalidDimension;
-  const Extents e = extents(layout, ta, tb, m, n, k);
-  size_t a_max = 0, b_max = 0, c_max = 0;
-  for (size_t i = 0; i < batch_count; ++i) {
-    if (a_offsets[i] > a_max) a_max = a_offsets[i];
-    if (b_offsets[i] > b_max) b_max = b_offsets[i];
-    if (c_offsets[i] > c_max) c_max = c_offsets[i];
-  }
-  // As in the reference, the leading dimensions of A and B are deliberately not tested for this routine.
-  int st = test_matrix(e.a_one, e.a_two, a, a_max, a_ld, elem, false, kInvalidLeadDimA, kInsufficientMemoryA,
-                       kInvalidMatrixA);
-  if (st) return st;
-  st = test_matrix(e.b_one, e.b_two, b, b_max, b_ld, elem, false, kInvalidLeadDimB, kInsufficientMemoryB,
-                   kInvalidMatrixB);
-  if (st) return st;
-  st = test_matrix(e.c_one, e.c_two, c, c_max, c_ld, elem, true, kInvalidLeadDimC, kInsufficientMemoryC,
-                   kInvalidMatrixC);
-  if (st) return st;
-
+  // Argument checks, normalisation and the per-batch tables (three offset tables, then alphas and betas converted
+  // to the kernel's compute type) are shared with the allocation-free entry point. As in the reference, the
+  // leading dimensions of A and B are deliberately not tested for this routine.
+  std::vector<unsigned char> host(3 * sizeof(long long) * batch_count + 16 + 2 * (16 * batch_count + 16));
   GemmDesc d = {};
-  d.dtype = dtype;
-  normalise(d, layout, ta, tb, m, n, k, a, a_ld, b, b_ld, c, c_ld, e);
-  const bool swapped = (layout == kRowMajor);
-  d.batch = static_cast<long long>(batch_count);
-  d.force_small = force_small_family(dtype, m, n, k);
-
-  // Stage the per-batch tables into one block: three offset tables, then alphas and betas converted to the
-  // kernel's compute type (float for half and single, double, or (re, im) pairs).
-  const size_t scalar_bytes = (dtype == 16 || dtype == 32) ? 4 : (dtype == 64 || dtype == 3232) ? 8 : 16;
-  const size_t off_bytes = batch_count * sizeof(long long);
-  const size_t off_block = (3 * off_bytes + 15) / 16 * 16;  // keeps the scalar tables 16-byte aligned
-  const size_t sc_bytes = (batch_count * scalar_bytes + 15) / 16 * 16;
-  const size_t total = off_block + 2 * sc_bytes;
-  std::vector<unsigned char> host(total);
-  long long* h_a = reinterpret_cast<long long*>(host.data());
-  long long* h_b = h_a + batch_count;
-  long long* h_c = h_b + batch_count;
-  unsigned char* h_alpha = host.data() + off_block;
-  unsigned char* h_beta = h_alpha + sc_bytes;
-  bool offsets_aligned = true;
-  for (size_t i = 0; i < batch_count; ++i) {
-    h_a[i] = static_cast<long long>(swapped ? b_offsets[i] : a_offsets[i]);
-    h_b[i] = static_cast<long long>(swapped ? a_offsets[i] : b_offsets[i]);
-    h_c[i] = static_cast<long long>(c_offsets[i]);
-    if ((a_offsets[i] | b_offsets[i] | c_offsets[i]) & 3) offsets_aligned = false;
-    double al[2], be[2];
-    read_scalar(dtype, alphas, i, al);
-    read_scalar(dtype, betas, i, be);
-    if (dtype == 16 || dtype == 32) {
-      reinterpret_cast<float*>(h_alpha)[i] = static_cast<float>(al[0]);
-      reinterpret_cast<float*>(h_beta)[i] = static_cast<float>(be[0]);
-    } else if (dtype == 64) {
-      reinterpret_cast<double*>(h_alpha)[i] = al[0];
-      reinterpret_cast<double*>(h_beta)[i] = be[0];
-    } else if (dtype == 3232) {
-      reinterpret_cast<float*>(h_alpha)[2 * i] = static_cast<float>(al[0]);
-      reinterpret_cast<float*>(h_alpha)[2 * i + 1] = static_cast<float>(al[1]);
-      reinterpret_cast<float*>(h_beta)[2 * i] = static_cast<float>(be[0]);
-      reinterpret_cast<float*>(h_beta)[2 * i + 1] = static_cast<float>(be[1]);
-    } else {
-      reinterpret_cast<double*>(h_alpha)[2 * i] = al[0];
-      reinterpret_cast<double*>(h_alpha)[2 * i + 1] = al[1];
-      reinterpret_cast<double*>(h_beta)[2 * i] = be[0];
-      reinterpret_cast<double*>(h_beta)[2 * i + 1] = be[1];
-    }
-  }
-  d.tables_aligned4 = offsets_aligned ? 1 : 0;
+  BatchedTables tables = {};
+  const int st = prepare_batched(dtype, layout, ta, tb, m, n, k, alphas, a, a_offsets, a_ld, b, b_offsets, b_ld, betas,
+                                 c, c_offsets, c_ld, batch_count, host.data(), host.size(), &d, &tables);
+  if (st != kSuccess) return st;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!async) {
@@ -546,14 +507,10 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
   // Stream-ordered scratch: allocated, filled, used and released in stream order, so concurrent calls on
   // different streams never share it. The host block is pageable, so the copy has left it when the call returns.
   unsigned char* dev = nullptr;
-  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&dev), total, s);
-  if (err == cudaSuccess) err = cudaMemcpyAsync(dev, host.data(), total, cudaMemcpyHostToDevice, s);
+  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&dev), tables.total, s);
+  if (err == cudaSuccess) err = cudaMemcpyAsync(dev, host.data(), tables.total, cudaMemcpyHostToDevice, s);
   if (err == cudaSuccess) {
-    d.a_offs = reinterpret_cast<const long long*>(dev);
-    d.b_offs = d.a_offs + batch_count;
-    d.c_offs = d.b_offs + batch_count;
-    d.alphas = dev + off_block;
-    d.betas = dev + off_block + sc_bytes;
+    patch_batched_tables(&d, tables, dev);
     err = dispatch(d, s);
   }
   if (dev) {
@@ -565,7 +522,7 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
     std::fprintf(stderr, "b200blas: CUDA error %d (%s)\n", static_cast<int>(err), cudaGetErrorString(err));
     return static_cast<int>(err);
   }
-  return kSuccess;
+  return tensor_core_status(async);
 }
 
 extern "C" int b200blas_convgemm(int dtype, int kernel_mode, size_t channels, size_t height, size_t width,

@@ -37,6 +37,7 @@ struct GemmDesc {
   ConvGeom conv;
   int force_small;                // selection-table override: use the small-tile family
   int tables_aligned4;            // every entry of the per-batch offset tables is a multiple of 4 elements
+  int uniform_strides;            // the offset tables are evenly spaced: a_off / a_stride etc. describe them too
 };
 
 }  // namespace b200

@@ -22,7 +22,7 @@
 #include <stdint.h>
 
 
-#include "../driver_api.h"
+#include "../tc_host.h"
 #include "launchers.h"
 
 namespace b200 {
@@ -53,6 +53,11 @@ struct TcParams {
   int k_blocks;
   float alpha, beta;
   int raster_group;     // m-tiles per rasterisation group
+  // batch: tiles of problem z follow those of problem z - 1; operands shared by all problems have *_batched == 0
+  int batches, a_batched, b_batched;
+  long long c_stride;
+  const float* alphas;  // per-problem scalars (offset-table calls), or null
+  const float* betas;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -99,11 +104,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+// Operand maps carry the batch as third coordinate (always 0 for a single problem).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
@@ -204,7 +210,8 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * p.batches;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -238,7 +245,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(p, tile, tm, tn);
+        const int z = tile / tiles_per_problem;
+        tile_coords(p, tile - z * tiles_per_problem, tm, tn);
+        const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
@@ -247,16 +256,16 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (A_MN) {  // column blocks of 64 rows x 64 k = 8 KB each
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(a_dst + j * 8192, &map_a, full_bar(stage), tm * BM + j * 64, kb * BK);
+              tma_load_3d(a_dst + j * 8192, &map_a, full_bar(stage), tm * BM + j * 64, kb * BK, az);
           } else {
-            tma_load_2d(a_dst, &map_a, full_bar(stage), kb * BK, tm * BM);
+            tma_load_3d(a_dst, &map_a, full_bar(stage), kb * BK, tm * BM, az);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * 8192, &map_b, full_bar(stage), tn * BN + j * 64, kb * BK);
+              tma_load_3d(b_dst + j * 8192, &map_b, full_bar(stage), tn * BN + j * 64, kb * BK, bz);
           } else {
-            tma_load_2d(b_dst, &map_b, full_bar(stage), kb * BK, tn * BN);
+            tma_load_3d(b_dst, &map_b, full_bar(stage), kb * BK, tn * BN, bz);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -315,10 +324,14 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
     int local = 0;
     bool ok = true;
-    const bool use_beta = p.beta != 0.f;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       int tm, tn;
-      tile_coords(p, tile, tm, tn);
+      const int z = tile / tiles_per_problem;
+      tile_coords(p, tile - z * tiles_per_problem, tm, tn);
+      const float alpha = p.alphas ? p.alphas[z] : p.alpha;
+      const float beta = p.betas ? p.betas[z] : p.beta;
+      const bool use_beta = beta != 0.f;
+      __half* const c_base = p.c + z * p.c_stride;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u);
@@ -335,12 +348,12 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t r[32];
         tmem_ld_32cols(t_row + cb * 32, r);
         if (row_ok) {
-          __half* cptr = p.c + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
+          __half* cptr = c_base + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + cb * 32 + j < p.n) {
-              float v = p.alpha * __uint_as_float(r[j]);
-              if (use_beta) v += p.beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
+              float v = alpha * __uint_as_float(r[j]);
+              if (use_beta) v += beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
               cptr[static_cast<long long>(j) * p.ldc] = __float2half_rn(v);
             }
           }
@@ -358,22 +371,6 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
-}
-
-bool encode_operand_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows,
-                        bool mn_contig) {
-  const DriverApi& drv = driver_api();
-  if (!drv.ok) return false;
-  // K-contiguous: map {K, rows}, box {64 k, box_rows}. M/N-contiguous: map {rows, K}, box {64 rows, 64 k}.
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_contig ? rows : k), static_cast<cuuint64_t>(mn_contig ? k : rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(mn_contig ? BK : box_rows)};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
-                                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
 }
 
 template <bool A_MN, bool B_MN>
@@ -399,21 +396,29 @@ cudaError_t tc_f16_status(unsigned int out[4], bool clear) {
 }
 
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 16 || d.is_conv || d.batch != 1 || d.force_small) return cudaErrorNotSupported;
+  if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
+  const BatchWalk walk = batch_walk(d);
+  if (!walk.ok) return cudaErrorNotSupported;
   if (d.m < 128 || d.n < 64 || d.k < 64) return cudaErrorNotSupported;
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const __half* a = static_cast<const __half*>(d.a) + d.a_off;
   const __half* b = static_cast<const __half*>(d.b) + d.b_off;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
   if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorNotSupported;
-  // TMA strides must stay below 2^40 bytes
-  if (d.lda * 2 >= (1LL << 40) || d.ldb * 2 >= (1LL << 40)) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
-  if (!encode_operand_map(&map_a, a, d.m, d.k, d.lda, BM, !d.a_kcontig)) return cudaErrorNotSupported;
-  if (!encode_operand_map(&map_b, b, d.n, d.k, d.ldb, BN, !d.b_kcontig)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_a, 2, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))
+    return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, 2, b, d.n, d.k, d.ldb, !d.b_kcontig, BN, walk.b_batches, walk.b_stride))
+    return cudaErrorNotSupported;
 
   TcParams p;
+  p.batches = walk.batches;
+  p.a_batched = walk.a_batches > 1;
+  p.b_batched = walk.b_batches > 1;
+  p.c_stride = walk.c_stride;
+  p.alphas = static_cast<const float*>(d.alphas);
+  p.betas = static_cast<const float*>(d.betas);
   p.c = static_cast<__half*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m);
@@ -434,7 +439,7 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
   if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
   const int sm_count = sm_counts[dev];
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   int sms = sm_count;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();

@@ -23,7 +23,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "../driver_api.h"
+#include "../tc_host.h"
 #include "launchers.h"
 #include "tc_common.cuh"
 
@@ -56,6 +56,11 @@ struct PairParams {
   int k_blocks;
   float alpha, beta;
   int raster_group;
+  // batch: tiles of problem z follow those of problem z - 1; operands shared by all problems have *_batched == 0
+  int batches, a_batched, b_batched;
+  long long c_stride;
+  const float* alphas;  // per-problem scalars (offset-table calls), or null
+  const float* betas;
 };
 
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -102,7 +107,8 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * p.batches;
   const int pair_index = blockIdx.x >> 1;
   const int pair_count = gridDim.x >> 1;
 
@@ -138,9 +144,11 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       bool ok = true;
       for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count) {
         int tm, tn;
-        tile_coords(p, tile, tm, tn);
+        const int z = tile / tiles_per_problem;
+        tile_coords(p, tile - z * tiles_per_problem, tm, tn);
         const int a_row0 = tm * 2 * BM + static_cast<int>(rank) * BM;
         const int b_row0 = tn * BN + static_cast<int>(rank) * BN_HALF;
+        const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, g_pair_status)) { ok = false; break; }
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
@@ -150,16 +158,16 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d_pair(a_dst + j * 8192, &map_a, lead_full, a_row0 + j * 64, kb * BK);
+              tma_load_3d_pair(a_dst + j * 8192, &map_a, lead_full, a_row0 + j * 64, kb * BK, az);
           } else {
-            tma_load_2d_pair(a_dst, &map_a, lead_full, kb * BK, a_row0);
+            tma_load_3d_pair(a_dst, &map_a, lead_full, kb * BK, a_row0, az);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN_HALF / 64; ++j)
-              tma_load_2d_pair(b_dst + j * 8192, &map_b, lead_full, b_row0 + j * 64, kb * BK);
+              tma_load_3d_pair(b_dst + j * 8192, &map_b, lead_full, b_row0 + j * 64, kb * BK, bz);
           } else {
-            tma_load_2d_pair(b_dst, &map_b, lead_full, kb * BK, b_row0);
+            tma_load_3d_pair(b_dst, &map_b, lead_full, kb * BK, b_row0, bz);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -210,10 +218,14 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int quad = warp & 3;
     int local = 0;
     bool ok = true;
-    const bool use_beta = p.beta != 0.f;
     for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count, ++local) {
       int tm, tn;
-      tile_coords(p, tile, tm, tn);
+      const int z = tile / tiles_per_problem;
+      tile_coords(p, tile - z * tiles_per_problem, tm, tn);
+      const float alpha = p.alphas ? p.alphas[z] : p.alpha;
+      const float beta = p.betas ? p.betas[z] : p.beta;
+      const bool use_beta = beta != 0.f;
+      __half* const c_base = p.c + z * p.c_stride;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_pair_status);
@@ -230,12 +242,12 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         uint32_t r[32];
         tmem_ld_32cols(t_row + cb * 32, r);
         if (row_ok) {
-          __half* cptr = p.c + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
+          __half* cptr = c_base + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + cb * 32 + j < p.n) {
-              float v = p.alpha * __uint_as_float(r[j]);
-              if (use_beta) v += p.beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
+              float v = alpha * __uint_as_float(r[j]);
+              if (use_beta) v += beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
               cptr[static_cast<long long>(j) * p.ldc] = __float2half_rn(v);
             }
           }
@@ -254,19 +266,6 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
-}
-
-bool encode_pair_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, bool mn_contig) {
-  const DriverApi& drv = driver_api();
-  if (!drv.ok) return false;
-  // K-contiguous: map {K, rows}, box {64 k, 128 rows}. M/N-contiguous: map {rows, K}, box {64 rows, 64 k}.
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_contig ? rows : k), static_cast<cuuint64_t>(mn_contig ? k : rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(mn_contig ? BK : 128)};
-  const cuuint32_t estr[2] = {1, 1};
-  return drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Number of CTA pairs the device can hold at once (one CTA per SM; pairs must sit in one GPC).
@@ -325,7 +324,9 @@ cudaError_t tc_f16_pair_status(unsigned int out[4], bool clear) {
 }
 
 cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 16 || d.is_conv || d.batch != 1 || d.force_small) return cudaErrorNotSupported;
+  if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
+  const BatchWalk walk = batch_walk(d);
+  if (!walk.ok) return cudaErrorNotSupported;
   // B200BLAS_HGEMM=single keeps the one-CTA-per-tile kernel
   static const bool forced_single = [] {
     const char* v = std::getenv("B200BLAS_HGEMM");
@@ -338,9 +339,14 @@ cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const cha
   const __half* b = static_cast<const __half*>(d.b) + d.b_off;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
   if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorNotSupported;
-  if (d.lda * 2 >= (1LL << 40) || d.ldb * 2 >= (1LL << 40)) return cudaErrorNotSupported;
 
   PairParams p;
+  p.batches = walk.batches;
+  p.a_batched = walk.a_batches > 1;
+  p.b_batched = walk.b_batches > 1;
+  p.c_stride = walk.c_stride;
+  p.alphas = static_cast<const float*>(d.alphas);
+  p.betas = static_cast<const float*>(d.betas);
   p.c = static_cast<__half*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m);
@@ -352,16 +358,18 @@ cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const cha
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 8;
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   // Half-empty pair tiles waste a whole SM: leave problems whose last row of pair tiles is at most half full, and
   // that have few tiles, to the single-CTA kernel.
-  const long long single_tiles = ((d.m + BM - 1) / BM) * p.tiles_n;
+  const long long single_tiles = ((d.m + BM - 1) / BM) * p.tiles_n * p.batches;
   if (single_tiles < 2 * tiles && tiles < 148) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
-  if (!encode_pair_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig)) return cudaErrorNotSupported;
-  if (!encode_pair_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_a, 2, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))
+    return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, 2, b, d.n, d.k, d.ldb, !d.b_kcontig, BN_HALF, walk.b_batches, walk.b_stride))
+    return cudaErrorNotSupported;
 
   *name = "tc_f16_pair_256x256x64";
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;

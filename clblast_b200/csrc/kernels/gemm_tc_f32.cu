@@ -31,7 +31,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "../driver_api.h"
+#include "../tc_host.h"
 #include "launchers.h"
 #include "tc_common.cuh"
 
@@ -61,6 +61,11 @@ struct Tc32Params {
   int tiles_m, tiles_n, k_blocks;
   float alpha, beta;
   int raster_group;
+  // GEMM batch: tiles of problem z follow those of problem z - 1; operands shared by all problems have *_batched == 0
+  int batches, a_batched, b_batched;
+  long long a_stride, b_stride, gemm_c_stride;
+  const float* alphas;  // per-problem scalars (offset-table calls), or null
+  const float* betas;
   // gathered operands (no TMA): element pointers and leading dimensions
   const float* a;
   const float* b;
@@ -130,7 +135,13 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n * (CONV ? p.batch : 1);
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * (CONV ? p.batch : p.batches);
+  // GEMM tiles: problem index, then the rasterised position inside the problem
+  auto gemm_tile = [&](int tile, int& tm, int& tn, int& z) {
+    z = tile / tiles_per_problem;
+    tile_coords(p, tile - z * tiles_per_problem, tm, tn);
+  };
   // register budgets (split, drain): the convolution variant prefetches its gather in registers and drains 64
   // columns per thread
   constexpr int SPLIT_REGS = (CONV || GATHER) ? 88 : 56;
@@ -173,8 +184,9 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn, image_index = 0;
-        if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else tile_coords(p, tile, tm, tn);
+        int tm, tn, image_index = 0, z = 0;
+        if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else gemm_tile(tile, tm, tn, z);
+        const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_status)) { ok = false; break; }
           if (GATHER) {
@@ -188,16 +200,16 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 32; ++j)
-              tma_load_2d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, kb * BK);
+              tma_load_3d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, kb * BK, az);
           } else {
-            tma_load_2d(a_main(stage), &map_a, raw_full(stage), kb * BK, tm * BM);
+            tma_load_3d(a_main(stage), &map_a, raw_full(stage), kb * BK, tm * BM, az);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j)
-              tma_load_2d(b_main(stage) + j * 4096, &map_b, raw_full(stage), tn * BN + j * 32, kb * BK);
+              tma_load_3d(b_main(stage) + j * 4096, &map_b, raw_full(stage), tn * BN + j * 32, kb * BK, bz);
           } else {
-            tma_load_2d(b_main(stage), &map_b, raw_full(stage), kb * BK, tn * BN);
+            tma_load_3d(b_main(stage), &map_b, raw_full(stage), kb * BK, tn * BN, bz);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -266,10 +278,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int half = (warp - 12) >> 2;
     int chunk_index = 0;
     bool ok = true;
-    const bool use_beta = p.beta != 0.f;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int tm, tn, image_index = 0;
-      if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else tile_coords(p, tile, tm, tn);
+      int tm, tn, image_index = 0, z = 0;
+      if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else gemm_tile(tile, tm, tn, z);
+      const float alpha = (!CONV && p.alphas) ? p.alphas[z] : p.alpha;
+      const float beta = (!CONV && p.betas) ? p.betas[z] : p.beta;
+      const bool use_beta = beta != 0.f;
       float acc[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) acc[j] = 0.f;
@@ -297,12 +311,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
       if (row < p.m) {
-        float* cptr = p.c + (CONV ? image_index * p.c_stride : 0) + static_cast<long long>(col0) * p.ldc + row;
+        float* cptr = p.c + (CONV ? image_index * p.c_stride : z * p.gemm_c_stride) + static_cast<long long>(col0) * p.ldc + row;
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) {
           if (col0 + j < p.n) {
-            float v = __fmul_rn(p.alpha, acc[j]);
-            if (use_beta) v = fmaf(p.beta, cptr[static_cast<long long>(j) * p.ldc], v);
+            float v = __fmul_rn(alpha, acc[j]);
+            if (use_beta) v = fmaf(beta, cptr[static_cast<long long>(j) * p.ldc], v);
             cptr[static_cast<long long>(j) * p.ldc] = v;
           }
         }
@@ -368,7 +382,10 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       };
-      if (GATHER) tile_coords(p, tile, tm, tn);
+      int z = 0;
+      if (GATHER) gemm_tile(tile, tm, tn, z);
+      const float* const a_src = p.a + (p.a_batched ? z * p.a_stride : 0);
+      const float* const b_src = p.b + (p.b_batched ? z * p.b_stride : 0);
       // One operand tile of 128 rows x 32 k. MN-contiguous: value j sits at k = sw + 8 (j / 4), row 32 (j % 4) + lane.
       // K-contiguous: value j sits at row sw + 8 j, k = lane.
       auto gather_plain = [&](float (&v)[GATHER ? 16 : 1], const float* src, long long ld, bool mn_major, int row0,
@@ -413,8 +430,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       };
       if (CONV) gather(0);
       if (GATHER) {
-        gather_plain(ga, p.a, p.lda, A_MN, tm * BM, p.m, 0);
-        gather_plain(gb, p.b, p.ldb, B_MN, tn * BN, p.n, 0);
+        gather_plain(ga, a_src, p.lda, A_MN, tm * BM, p.m, 0);
+        gather_plain(gb, b_src, p.ldb, B_MN, tn * BN, p.n, 0);
       }
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_status);
@@ -448,8 +465,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           store_plain(ga, stage_ptr, stage_ptr + C::A_BYTES + C::B_BYTES, A_MN);
           store_plain(gb, stage_ptr + C::A_BYTES, stage_ptr + 2 * C::A_BYTES + C::B_BYTES, B_MN);
           if (kb + 1 < p.k_blocks) {  // in flight while the tensor cores work on this stage
-            gather_plain(ga, p.a, p.lda, A_MN, tm * BM, p.m, kb + 1);
-            gather_plain(gb, p.b, p.ldb, B_MN, tn * BN, p.n, kb + 1);
+            gather_plain(ga, a_src, p.lda, A_MN, tm * BM, p.m, kb + 1);
+            gather_plain(gb, b_src, p.ldb, B_MN, tn * BN, p.n, kb + 1);
           }
         }
 #pragma unroll 4
@@ -475,29 +492,6 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-}
-
-// K-contiguous operand: 2-D map {K, rows}, box {32, box_rows}. M/N-contiguous operand: map {rows, K}, box {32, 32}.
-bool encode_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, bool mn_contig,
-                int box_rows) {
-  const DriverApi& drv = driver_api();
-  if (!drv.ok) return false;
-  cuuint64_t dims[2];
-  cuuint32_t box[2];
-  if (mn_contig) {
-    dims[0] = static_cast<cuuint64_t>(rows); dims[1] = static_cast<cuuint64_t>(k);
-    box[0] = 32; box[1] = 32;
-  } else {
-    dims[0] = static_cast<cuuint64_t>(k); dims[1] = static_cast<cuuint64_t>(rows);
-    box[0] = 32; box[1] = static_cast<cuuint32_t>(box_rows);
-  }
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-  const cuuint32_t estr[2] = {1, 1};
-  // M/N-major 32-bit operands must sit in shared memory with the 32-byte-chunk flavour of the 128-byte swizzle.
-  const CUtensorMapSwizzle swizzle = mn_contig ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
-  return drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
-                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE = kTma>
@@ -527,7 +521,9 @@ cudaError_t tc_f32_status(unsigned int out[4], bool clear) {
 }
 
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.batch != 1 || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  const BatchWalk walk = batch_walk(d);
+  if (!walk.ok) return cudaErrorNotSupported;
   // Static selection: the tensor-core path pays off once there are enough 128x256 tiles and K blocks to fill the
   // pipeline; smaller problems keep the k-ascending CUDA-core kernel. B200BLAS_SGEMM=ffma forces the latter.
   static const bool forced_ffma = [] {
@@ -536,13 +532,15 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   }();
   if (forced_ffma) return cudaErrorNotSupported;
   if (d.m < 256 || d.n < 256 || d.k < 128) return cudaErrorNotSupported;
-  if (static_cast<double>(d.m) * d.n * d.k < 134217728.0) return cudaErrorNotSupported;  // 512^3
+  if (static_cast<double>(d.m) * d.n * d.k * walk.batches < 134217728.0) return cudaErrorNotSupported;  // 512^3
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
   // TMA needs 16-byte aligned rows; everything else is gathered with plain loads by the split warps.
   const bool gathered = (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
-                        (d.lda % 4) || (d.ldb % 4) || d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40);
+                        (d.lda % 4) || (d.ldb % 4) || d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40) ||
+                        (walk.a_stride % 4) || (walk.b_stride % 4) || walk.a_stride * 4 >= (1LL << 40) ||
+                        walk.b_stride * 4 >= (1LL << 40);
 
   // Tile width: 256 columns amortise the operand traffic best; 128 columns give twice as many tiles and one more
   // pipeline stage, which wins while 256-wide tiles would leave SMs idle.
@@ -551,7 +549,7 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
   if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256);
+  const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256) * walk.batches;
   const int bn = (!gathered && tiles_wide >= 2LL * sm_counts[dev]) ? 256 : 128;
 
   CUtensorMap map_a, map_b;
@@ -559,13 +557,21 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
     std::memset(&map_a, 0, sizeof(map_a));
     std::memset(&map_b, 0, sizeof(map_b));
   } else {
-    if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig, BM)) return cudaErrorNotSupported;
-    if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig, bn)) return cudaErrorNotSupported;
+    if (!encode_operand_map(&map_a, 4, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))
+      return cudaErrorNotSupported;
+    if (!encode_operand_map(&map_b, 4, b, d.n, d.k, d.ldb, !d.b_kcontig, bn, walk.b_batches, walk.b_stride))
+      return cudaErrorNotSupported;
   }
 
   Tc32Params p = {};
   p.a = a; p.b = b;
   p.lda = d.lda; p.ldb = d.ldb;
+  p.batches = walk.batches;
+  p.a_batched = walk.a_batches > 1;
+  p.b_batched = walk.b_batches > 1;
+  p.a_stride = walk.a_stride; p.b_stride = walk.b_stride; p.gemm_c_stride = walk.c_stride;
+  p.alphas = static_cast<const float*>(d.alphas);
+  p.betas = static_cast<const float*>(d.betas);
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
@@ -576,7 +582,7 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 16;
 
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   int sms = sm_counts[dev];
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
@@ -626,7 +632,7 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   if (d.m < 128 || d.n < 32 || d.k < 64 || tiles < 64 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
 
   CUtensorMap map_b;
-  if (!encode_map(&map_b, weights, d.n, d.k, d.ldb, false, BN)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, 4, weights, d.n, d.k, d.ldb, false, BN, 1, 0)) return cudaErrorNotSupported;
 
   Tc32Params p = {};
   p.c = static_cast<float*>(d.c) + d.c_off;

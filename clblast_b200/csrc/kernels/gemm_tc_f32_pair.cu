@@ -22,7 +22,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "../driver_api.h"
+#include "../tc_host.h"
 #include "launchers.h"
 #include "tc_common.cuh"
 
@@ -59,6 +59,11 @@ struct PairParams {
   int tiles_m, tiles_n, k_blocks;  // 256 x 256 pair tiles
   float alpha, beta;
   int raster_group;
+  // batch: tiles of problem z follow those of problem z - 1; operands shared by all problems have *_batched == 0
+  int batches, a_batched, b_batched;
+  long long c_stride;
+  const float* alphas;  // per-problem scalars (offset-table calls), or null
+  const float* betas;
 };
 
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& tm, int& tn) {
@@ -95,7 +100,8 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_problem * p.batches;
   const int pair_index = blockIdx.x >> 1;
   const int pair_count = gridDim.x >> 1;
 
@@ -136,25 +142,27 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         bool ok = true;
         for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count) {
           int tm, tn;
-          tile_coords(p, tile, tm, tn);
+          const int z = tile / tiles_per_problem;
+          tile_coords(p, tile - z * tiles_per_problem, tm, tn);
           const int a_row0 = tm * 2 * BM + static_cast<int>(rank) * BM;
           const int b_row0 = tn * BN + static_cast<int>(rank) * BN_HALF;
+          const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
           for (int kb = 0; kb < p.k_blocks; ++kb) {
             if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_pair_status)) { ok = false; break; }
             mbar_arrive_expect_tx(raw_full(stage), A_BYTES + B_BYTES);
             if (A_MN) {
 #pragma unroll
               for (int j = 0; j < BM / 32; ++j)
-                tma_load_2d(a_main(stage) + j * 4096, &map_a, raw_full(stage), a_row0 + j * 32, kb * BK);
+                tma_load_3d(a_main(stage) + j * 4096, &map_a, raw_full(stage), a_row0 + j * 32, kb * BK, az);
             } else {
-              tma_load_2d(a_main(stage), &map_a, raw_full(stage), kb * BK, a_row0);
+              tma_load_3d(a_main(stage), &map_a, raw_full(stage), kb * BK, a_row0, az);
             }
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN_HALF / 32; ++j)
-                tma_load_2d(b_main(stage) + j * 4096, &map_b, raw_full(stage), b_row0 + j * 32, kb * BK);
+                tma_load_3d(b_main(stage) + j * 4096, &map_b, raw_full(stage), b_row0 + j * 32, kb * BK, bz);
             } else {
-              tma_load_2d(b_main(stage), &map_b, raw_full(stage), kb * BK, b_row0);
+              tma_load_3d(b_main(stage), &map_b, raw_full(stage), kb * BK, b_row0, bz);
             }
             ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -226,11 +234,14 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int half = (warp - 12) >> 2;
     int chunk_index = 0;
     bool ok = true;
-    const bool use_beta = p.beta != 0.f;
     const uint32_t lead_free0 = map_to_cta(part_free(0), 0), lead_free1 = map_to_cta(part_free(1), 0);
     for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count) {
       int tm, tn;
-      tile_coords(p, tile, tm, tn);
+      const int z = tile / tiles_per_problem;
+      tile_coords(p, tile - z * tiles_per_problem, tm, tn);
+      const float alpha = p.alphas ? p.alphas[z] : p.alpha;
+      const float beta = p.betas ? p.betas[z] : p.beta;
+      const bool use_beta = beta != 0.f;
       float acc[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) acc[j] = 0.f;
@@ -258,12 +269,12 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
       if (row < p.m) {
-        float* cptr = p.c + static_cast<long long>(col0) * p.ldc + row;
+        float* cptr = p.c + z * p.c_stride + static_cast<long long>(col0) * p.ldc + row;
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) {
           if (col0 + j < p.n) {
-            float v = __fmul_rn(p.alpha, acc[j]);
-            if (use_beta) v = fmaf(p.beta, cptr[static_cast<long long>(j) * p.ldc], v);
+            float v = __fmul_rn(alpha, acc[j]);
+            if (use_beta) v = fmaf(beta, cptr[static_cast<long long>(j) * p.ldc], v);
             cptr[static_cast<long long>(j) * p.ldc] = v;
           }
         }
@@ -308,27 +319,6 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     tcgen05_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
-}
-
-// K-contiguous operand: 2-D map {K, rows}, box {32, 128}. M/N-contiguous operand: map {rows, K}, box {32, 32}.
-bool encode_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, bool mn_contig) {
-  const DriverApi& drv = driver_api();
-  if (!drv.ok) return false;
-  cuuint64_t dims[2];
-  cuuint32_t box[2];
-  if (mn_contig) {
-    dims[0] = static_cast<cuuint64_t>(rows); dims[1] = static_cast<cuuint64_t>(k);
-    box[0] = 32; box[1] = 32;
-  } else {
-    dims[0] = static_cast<cuuint64_t>(k); dims[1] = static_cast<cuuint64_t>(rows);
-    box[0] = 32; box[1] = 128;
-  }
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapSwizzle swizzle = mn_contig ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
-  return drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
-                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <bool A_MN, bool B_MN>
@@ -391,7 +381,9 @@ cudaError_t tc_f32_pair_status(unsigned int out[4], bool clear) {
 }
 
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.batch != 1 || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  const BatchWalk walk = batch_walk(d);
+  if (!walk.ok) return cudaErrorNotSupported;
   // B200BLAS_SGEMM=ffma forces the CUDA-core kernel, =single the one-CTA-per-tile tensor-core kernels
   static const bool disabled = [] {
     const char* v = std::getenv("B200BLAS_SGEMM");
@@ -404,9 +396,15 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   const float* b = static_cast<const float*>(d.b) + d.b_off;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return cudaErrorNotSupported;
   if ((d.lda % 4) || (d.ldb % 4)) return cudaErrorNotSupported;
-  if (d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40)) return cudaErrorNotSupported;
+  if ((walk.a_stride % 4) || (walk.b_stride % 4)) return cudaErrorNotSupported;
 
   PairParams p;
+  p.batches = walk.batches;
+  p.a_batched = walk.a_batches > 1;
+  p.b_batched = walk.b_batches > 1;
+  p.c_stride = walk.c_stride;
+  p.alphas = static_cast<const float*>(d.alphas);
+  p.betas = static_cast<const float*>(d.betas);
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
@@ -416,14 +414,16 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 8;
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   // Enough 256 x 256 tiles to give every pair of SMs two: below that the 128-wide single-CTA tiles fill the
   // machine better.
   if (tiles < 148 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
-  if (!encode_map(&map_a, a, d.m, d.k, d.lda, !d.a_kcontig)) return cudaErrorNotSupported;
-  if (!encode_map(&map_b, b, d.n, d.k, d.ldb, !d.b_kcontig)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_a, 4, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))
+    return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, 4, b, d.n, d.k, d.ldb, !d.b_kcontig, BN_HALF, walk.b_batches, walk.b_stride))
+    return cudaErrorNotSupported;
 
   *name = "tc_f32_3xtf32_pair_256x256x32";
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
