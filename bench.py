@@ -61,6 +61,11 @@ WORKLOADS = {
                        alpha=1.0, beta=1.0, dist="uniform1", bound="hbm"),
     "batched_64x128x96": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=64, n=128, k=96, batch=2048,
                               alpha=1.0, beta=1.0, dist="uniform1", bound="hbm"),
+    # larger problems per batch entry run on the tensor cores (batch as third tensor-map dimension)
+    "hgemm_batched_1024x64": dict(kind="strided", precision=16, layout=ROW, ta=NO, tb=YES, m=1024, n=1024, k=1024,
+                                  batch=64, alpha=1.0, beta=0.0, dist="normal0.1", bound="tensor"),
+    "sgemm_batched_512x128": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=512, n=512, k=512,
+                                  batch=128, alpha=1.0, beta=0.0, dist="uniform1", bound="fp32"),
     "conv_56": dict(kind="conv", precision=32, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
                     num_kernels=128, batch=32, bound="fp32"),
 }
