@@ -233,7 +233,8 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   cudaError_t err;
   switch (d.dtype) {
     case 32:
-      err = d.is_conv ? launch_tc_conv_f32(d, stream, &name) : launch_small_batched_f32(d, stream, &name);
+      err = d.is_conv ? launch_tc_conv_f32(d, stream, &name) : launch_tc_f32_narrow(d, stream, &name);
+      if (err == cudaErrorNotSupported && !d.is_conv) err = launch_small_batched_f32(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_tc_f32_pair(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_tc_f32(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);

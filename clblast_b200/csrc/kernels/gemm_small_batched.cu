@@ -62,8 +62,9 @@ struct SmallLayout {
 
 // SETS = 2: the next problem is prefetched while the current one is computed (double buffering inside the CTA).
 // SETS = 1: one buffer set per CTA; two CTAs share an SM and overlap each other's loads and arithmetic.
-template <int BM, int BN, int KMAX, int TM, int TN, int GROUPS, int SETS, bool A_KC, bool B_KC>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, 2) gemm_small_batched_kernel(const SmallParams p) {
+// CTAS: resident CTAs per SM the launch is sized for (and the register bound that goes with it).
+template <int BM, int BN, int KMAX, int TM, int TN, int GROUPS, int SETS, int CTAS, bool A_KC, bool B_KC>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, CTAS) gemm_small_batched_kernel(const SmallParams p) {
   using L = SmallLayout<BM, BN, KMAX, A_KC, B_KC>;
   constexpr int NT = (BM / TM) * (BN / TN);
   extern __shared__ __align__(16) float smem[];
@@ -261,20 +262,20 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN) * GROUPS, 2) gemm_small_
   cp_async_wait<0>();
 }
 
-template <int BM, int BN, int KMAX, int TM, int TN, int GROUPS, int SETS>
+template <int BM, int BN, int KMAX, int TM, int TN, int GROUPS, int SETS, int CTAS = 2>
 struct SmallLauncher {
   template <bool A_KC, bool B_KC>
   static cudaError_t go(const SmallParams& p, cudaStream_t stream, int sm_count) {
     using L = SmallLayout<BM, BN, KMAX, A_KC, B_KC>;
     constexpr int SMEM = GROUPS * SETS * L::SET_FLOATS * static_cast<int>(sizeof(float));
-    static_assert(2 * SMEM <= 226 * 1024, "two CTAs must fit the shared memory of one SM");
-    auto kernel = gemm_small_batched_kernel<BM, BN, KMAX, TM, TN, GROUPS, SETS, A_KC, B_KC>;
+    static_assert(CTAS * SMEM <= 226 * 1024, "the resident CTAs must fit the shared memory of one SM");
+    auto kernel = gemm_small_batched_kernel<BM, BN, KMAX, TM, TN, GROUPS, SETS, CTAS, A_KC, B_KC>;
     {  // per-context attribute; contexts come and go, so it is set before every launch
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return e;
     }
     const long long ctas = (p.batch + GROUPS - 1) / GROUPS;
-    const long long resident = 2LL * sm_count;  // two CTAs per SM
+    const long long resident = static_cast<long long>(CTAS) * sm_count;
     const int grid = static_cast<int>(ctas < resident ? ctas : resident);
     constexpr int NT = (BM / TM) * (BN / TN) * GROUPS;
     kernel<<<grid, NT, SMEM, stream>>>(p);
@@ -333,12 +334,14 @@ cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, con
   if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
   if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
 
+  // Thread tiles of 4 x 4 (8 x 4 for the wide class) keep several warps per scheduler busy: with 8 x 8 tiles a
+  // scheduler had a single warp and issued at 0.42 instructions per cycle.
   if (fits_small) {
     *name = "small_batched_f32_32x32x32";
-    return SmallLauncher<32, 32, 32, 8, 8, 4, 2>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
+    return SmallLauncher<32, 32, 32, 4, 4, 1, 2, 8>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
   }
   *name = "small_batched_f32_64x128x96";
-  return SmallLauncher<64, 128, 96, 8, 8, 1, 1>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
+  return SmallLauncher<64, 128, 96, 8, 4, 1, 1>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
 }
 
 }  // namespace b200

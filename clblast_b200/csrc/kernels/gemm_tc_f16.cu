@@ -24,10 +24,13 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "tc_common.cuh"
 
 namespace b200 {
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128;      // MMA M: rows of op(A) per tile (TMEM lanes)
 constexpr int BN = 256;      // MMA N: columns of op(B) per tile (TMEM columns per accumulator)
@@ -40,7 +43,6 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of BN fp32 columns
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr long long WAIT_CYCLES = 4000000000LL;  // about two seconds at 2 GHz
 
 // [0] first timeout code seen (0 = none), [1] block that saw it, [2] role-specific detail.
 __device__ unsigned int g_tc_status[4];
@@ -59,123 +61,6 @@ struct TcParams {
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait. Returns false when the wait expired or another role already raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - start > WAIT_CYCLES) {
-        *abort_flag = 1;
-        if (atomicCAS(&g_tc_status[0], 0u, code) == 0u) {
-          g_tc_status[1] = blockIdx.x;
-          g_tc_status[2] = bar;
-        }
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-// Operand maps carry the batch as third coordinate (always 0 for a single problem).
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte swizzle:
-// start address / 16 in bits 0-13, leading byte offset (unused for swizzled K-major, set to 1) in bits 16-29,
-// stride byte offset = 1024 bytes (8 rows) / 16 in bits 32-45, descriptor version 1 in bits 46-47, layout type
-// 2 (128-byte swizzle) in bits 61-63.
-__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-// Same for an MN-major 16-bit tile: 128-byte rows of 64 elements (one per k), leading byte offset 8192 (next
-// 64-element column block), stride byte offset 1024 (next group of eight k).
-__device__ __forceinline__ uint64_t mnmajor_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-  d |= static_cast<uint64_t>(8192 >> 4) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
-// Instruction descriptor for kind::f16: fp32 accumulator (bits 4-5 = 1), A and B fp16 (0), both K-major (bits 15,
-// 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32cols(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // Tiles are walked in groups of `raster_group` m-tiles by all n-tiles, m fastest inside a group, so the CTAs
 // running at the same time share a small set of operand rows in L2.
@@ -223,13 +108,10 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(acc_empty_bar(a), 4);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_barrier_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -249,7 +131,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tile_coords(p, tile - z * tiles_per_problem, tm, tn);
         const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, g_tc_status)) { ok = false; break; }
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -280,14 +162,14 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           int s = stage - 1 - i;
           if (s < 0) s += STAGES;
           const uint32_t par = (s < stage) ? phase : (phase ^ 1u);
-          while (!mbar_try_wait(full_bar(s), par) && clock64() - start < WAIT_CYCLES / 8) {}
+          while (!mbar_try_wait(full_bar(s), par) && clock64() - start < kWaitCycles / 8) {}
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN) | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
+      constexpr uint32_t idesc = make_idesc(BM, BN, 0, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -295,19 +177,19 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u)) { ok = false; break; }
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u, g_tc_status)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u)) { ok = false; break; }
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u, g_tc_status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_BYTES;
           // K-major: 128-byte rows along K, advance 16 halves = 32 B per MMA. MN-major: one 128-byte row of 64
           // elements per k, swizzle atoms of eight k (1024 B, the stride offset), column blocks 8192 B apart (the
           // leading offset), advance 16 k = 2048 B per MMA.
-          const uint64_t da = A_MN ? mnmajor_sw128_desc(a_src) : kmajor_sw128_desc(a_src);
-          const uint64_t db = B_MN ? mnmajor_sw128_desc(b_src) : kmajor_sw128_desc(b_src);
+          const uint64_t da = smem_desc(a_src, A_MN ? 8192 : 16, 1024, kLayoutSw128);
+          const uint64_t db = smem_desc(b_src, B_MN ? 8192 : 16, 1024, kLayoutSw128);
           constexpr uint32_t a_step = A_MN ? (2048u >> 4) : 2u, b_step = B_MN ? (2048u >> 4) : 2u;
 #pragma unroll
           for (int ks = 0; ks < BK / UMMA_K; ++ks) {
@@ -334,7 +216,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       __half* const c_base = p.c + z * p.c_stride;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u);
+      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_tc_status);
       ok = __all_sync(0xffffffffu, ok);  // also reconverges the warp before the warp-wide TMEM loads
       if (!ok) break;
       tcgen05_fence_after();
@@ -369,7 +251,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 

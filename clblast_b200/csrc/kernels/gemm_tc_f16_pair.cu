@@ -63,17 +63,6 @@ struct PairParams {
   const float* betas;
 };
 
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& tm, int& tn) {
   const int per_group = p.raster_group * p.tiles_n;
   const int group = tile / per_group;

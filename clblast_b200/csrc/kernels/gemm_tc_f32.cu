@@ -66,6 +66,9 @@ struct Tc32Params {
   long long a_stride, b_stride, gemm_c_stride;
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
+  // The kernel computes the transposed problem (operands swapped by the launcher): element (row, col) of its tile
+  // goes to c[row * ldc + col], so each thread's results are contiguous in memory. c_vec4: 16-byte stores allowed.
+  int c_rowmajor, c_vec4;
   // gathered operands (no TMA): element pointers and leading dimensions
   const float* a;
   const float* b;
@@ -82,7 +85,7 @@ struct Cfg {
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // main (raw -> hi in place) and lo copies
-  static constexpr int STAGES = (BN == 256) ? 2 : 3;
+  static constexpr int STAGES = (BN == 256) ? 2 : (BN == 64) ? 4 : 3;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
@@ -310,7 +313,34 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok) break;
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
-      if (row < p.m) {
+      if (!CONV && p.c_rowmajor) {
+        if (row < p.m) {
+          float* cptr = p.c + z * p.gemm_c_stride + static_cast<long long>(row) * p.ldc + col0;
+          if (p.c_vec4 && col0 + BN / 2 <= p.n) {
+#pragma unroll
+            for (int j = 0; j < BN / 2; j += 4) {
+              float4 v;
+              v.x = __fmul_rn(alpha, acc[j]); v.y = __fmul_rn(alpha, acc[j + 1]);
+              v.z = __fmul_rn(alpha, acc[j + 2]); v.w = __fmul_rn(alpha, acc[j + 3]);
+              if (use_beta) {
+                const float4 old = *reinterpret_cast<const float4*>(cptr + j);
+                v.x = fmaf(beta, old.x, v.x); v.y = fmaf(beta, old.y, v.y);
+                v.z = fmaf(beta, old.z, v.z); v.w = fmaf(beta, old.w, v.w);
+              }
+              *reinterpret_cast<float4*>(cptr + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 2; ++j) {
+              if (col0 + j < p.n) {
+                float v = __fmul_rn(alpha, acc[j]);
+                if (use_beta) v = fmaf(beta, cptr[j], v);
+                cptr[j] = v;
+              }
+            }
+          }
+        }
+      } else if (row < p.m) {
         float* cptr = p.c + (CONV ? image_index * p.c_stride : z * p.gemm_c_stride) + static_cast<long long>(col0) * p.ldc + row;
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) {
@@ -614,6 +644,74 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   }
   return b_mn ? launch_variant<128, false, true>(map_a, map_b, p, grid, stream)
               : launch_variant<128, false, false>(map_a, map_b, p, grid, stream);
+}
+
+// Batches of problems with at most 64 rows (after layout normalisation) and enough columns to fill a 128-row tile:
+// the transposed problem C^T = op(B)^T op(A)^T is computed, one 128 x 64 tile per problem and 128 columns, so the
+// narrow dimension becomes the MMA's N. Such batches (2048 x 64x128x96 is the typical one) sit on the FP32 ridge of
+// the CUDA cores; on the tensor cores they are bound by HBM traffic alone.
+cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const char** name) {
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  static const bool forced_ffma = [] {
+    const char* v = std::getenv("B200BLAS_SGEMM");
+    return v != nullptr && std::strcmp(v, "ffma") == 0;
+  }();
+  if (forced_ffma) return cudaErrorNotSupported;
+  const BatchWalk walk = batch_walk(d);
+  if (!walk.ok) return cudaErrorNotSupported;
+  constexpr int BN = 64;
+  if (d.m > BN || d.m < 16 || d.n < 64 || d.k < 32 || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
+  const long long tiles = ((d.n + BM - 1) / BM) * walk.batches;
+  if (tiles < 148 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  if (static_cast<double>(d.m) * d.n * d.k * walk.batches < 134217728.0) return cudaErrorNotSupported;
+  const float* a = static_cast<const float*>(d.a) + d.a_off;
+  const float* b = static_cast<const float*>(d.b) + d.b_off;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (d.lda % 4) || (d.ldb % 4) ||
+      (walk.a_stride % 4) || (walk.b_stride % 4))
+    return cudaErrorNotSupported;
+
+  // operands swapped: the kernel's A (128-row tiles) is op(B)^T, its B (64 columns) is op(A)^T
+  CUtensorMap map_a, map_b;
+  if (!encode_operand_map(&map_a, 4, b, d.n, d.k, d.ldb, !d.b_kcontig, BM, walk.b_batches, walk.b_stride))
+    return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_b, 4, a, d.m, d.k, d.lda, !d.a_kcontig, BN, walk.a_batches, walk.a_stride))
+    return cudaErrorNotSupported;
+
+  Tc32Params p = {};
+  p.c = static_cast<float*>(d.c) + d.c_off;
+  p.ldc = d.ldc;
+  p.m = static_cast<int>(d.n); p.n = static_cast<int>(d.m); p.k = static_cast<int>(d.k);
+  p.tiles_m = static_cast<int>((d.n + BM - 1) / BM);
+  p.tiles_n = 1;
+  p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
+  p.alpha = static_cast<float>(d.alpha[0]);
+  p.beta = static_cast<float>(d.beta[0]);
+  p.raster_group = 16;
+  p.batches = walk.batches;
+  p.a_batched = walk.b_batches > 1;
+  p.b_batched = walk.a_batches > 1;
+  p.gemm_c_stride = walk.c_stride;
+  p.alphas = static_cast<const float*>(d.alphas);
+  p.betas = static_cast<const float*>(d.betas);
+  p.c_rowmajor = 1;
+  p.c_vec4 = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && d.ldc % 4 == 0 && walk.c_stride % 4 == 0) ? 1 : 0;
+
+  static int sm_counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
+  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  int sms = sm_counts[dev];
+  if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  *name = "tc_f32_3xtf32_narrow_128x64x32";
+  const bool a_mn = !d.b_kcontig, b_mn = !d.a_kcontig;
+  if (a_mn) {
+    return b_mn ? launch_variant<BN, true, true>(map_a, map_b, p, grid, stream)
+                : launch_variant<BN, true, false>(map_a, map_b, p, grid, stream);
+  }
+  return b_mn ? launch_variant<BN, false, true>(map_a, map_b, p, grid, stream)
+              : launch_variant<BN, false, false>(map_a, map_b, p, grid, stream);
 }
 
 cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {

@@ -31,6 +31,8 @@ cudaError_t tc_f32_status(unsigned int out[4], bool clear);
 // The same on CTA pairs (256 x 256 tiles shared by two SMs), tried first for large problems.
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name);
 cudaError_t tc_f32_pair_status(unsigned int out[4], bool clear);
+// Batches of narrow problems (at most 64 rows) on the same kernel, computed as the transposed problem.
+cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const char** name);
 // Tensor-core Convgemm (same kernel, op(A) gathered from the image by the split warps).
 cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 

@@ -78,7 +78,7 @@ def test_config4_small_batched_shapes(cuda, layout):
 @pytest.mark.parametrize("ta,tb", ((H.NO, H.NO), (H.NO, H.YES), (H.YES, H.NO), (H.YES, H.YES)))
 def test_streaming_small_batched_kernel(cuda, layout, ta, tb):
     """Large aligned batches of small fp32 problems take the cp.async streaming kernel; results must be bit-identical
-    to the reference-order oracle, like the generic kernel's."""
+    to the reference-order oracle, like the generic kernel's. The 64 x 128 x 96 class moves on to the tensor cores."""
     rng = np.random.default_rng(31)
     for (m, n, k), batch, (alpha, beta), pad in (((32, 32, 32), 301, (1.0, 1.0), 0), ((16, 24, 20), 600, (1.5, 0.0), 4),
                                                  ((64, 128, 96), 299, (1.0, 1.0), 0), ((60, 100, 64), 310, (0.5, 2.0), 8)):
@@ -89,9 +89,21 @@ def test_streaming_small_batched_kernel(cuda, layout, ta, tb):
                                    g["b_stride"], beta, dc, 0, g["c_ld"], g["c_stride"], batch)
         assert st == cb.StatusCode.kSuccess
         mm, nn = (m, n) if layout == H.COL else (n, m)   # extents after normalisation to a column-major C
+        got = H.to_host(32, dc)
+        if mm <= 64 and nn >= 64 and k >= 32 and mm * nn * k * batch >= 2 ** 27:
+            # narrow problems with enough columns go to the tensor cores as the transposed problem (3xTF32: fp32-level
+            # accuracy, not the reference's order of operations)
+            assert cb.last_kernel().startswith("tc_f32_3xtf32_narrow"), (cb.last_kernel(), m, n, k)
+            want = oracle.widen(32, g["c"])
+            for i in range(batch):
+                out = oracle.gemm_f64(32, layout, ta, tb, m, n, k, alpha, g["a"], i * g["a_stride"], g["a_ld"], g["b"],
+                                      i * g["b_stride"], g["b_ld"], beta, g["c"], i * g["c_stride"], g["c_ld"])
+                one = H.c_mask(layout, m, n, i * g["c_stride"], g["c_ld"], g["c"].size)
+                want[one] = out[one]
+            assert np.abs(got - want).max() <= 2.0 ** -20 * (abs(alpha) * k + abs(beta))
+            continue
         eligible = mm % 4 == 0 and ((mm <= 32 and nn <= 32 and k <= 32) or (mm <= 64 and nn <= 128 and k <= 96))
         assert cb.last_kernel().startswith("small_batched") == eligible, (cb.last_kernel(), m, n, k)
-        got = H.to_host(32, dc)
         want = g["c"].copy()
         for i in range(batch):
             oracle.gemm(32, layout, ta, tb, m, n, k, alpha, g["a"], i * g["a_stride"], g["a_ld"], g["b"],

@@ -117,3 +117,38 @@ def test_offset_table_batches(cuda, precision, expect, layout):
     single = call(offs["a"][3:4], offs["b"][2:3], offs["c"][5:6], 1)
     # one 384 x 512 x 136 problem is below the size at which single precision moves to the tensor cores
     assert single.startswith(expect if precision == 16 else "simt_"), single
+
+
+@pytest.mark.parametrize("layout,ta,tb", LAYOUTS)
+def test_narrow_problems_run_transposed_on_the_tensor_cores(cuda, layout, ta, tb):
+    """Batches whose problems have at most 64 rows of C (after layout normalisation) and at least 64 columns: the
+    kernel computes C^T = op(B)^T op(A)^T, so the narrow extent becomes the MMA's N. Ragged extents, K tail, a
+    leading dimension of C that rules out 16-byte stores, beta from zero and non-zero."""
+    rng = np.random.default_rng(8)
+    swap = layout == H.ROW
+    shape = lambda narrow, wide: (wide, narrow) if swap else (narrow, wide)
+    run_strided(cuda, rng, 32, layout, ta, tb, *shape(64, 128), 96, 300, 1.0, 1.0, 0, 0, "tc_f32_3xtf32_narrow")
+    run_strided(cuda, rng, 32, layout, ta, tb, *shape(48, 200), 72, 240, -1.5, 0.5, 4, 8, "tc_f32_3xtf32_narrow")
+    run_strided(cuda, rng, 32, layout, ta, tb, *shape(20, 136), 100, 600, 2.0, 0.0, 4, 4, "tc_f32_3xtf32_narrow")
+
+
+def test_narrow_problems_with_offset_tables_and_odd_c_stride(cuda):
+    torch = cuda
+    rng = np.random.default_rng(9)
+    m, n, k, batch = 64, 128, 96, 320
+    g = strided_case(rng, 32, H.COL, H.NO, H.NO, m, n, k, batch, 4, 0, -1.0, 1.0)
+    g["c_ld"] = m + 1   # C needs no alignment: scalar stores
+    g["c_stride"] = g["c_ld"] * n + 3
+    g["c"] = H.rand_buffer(rng, 32, 5 + g["c_stride"] * batch + H.CANARY, -1.0, 1.0)
+    alphas = [1.0 + 0.01 * i for i in range(batch)]
+    betas = [0.0 if i % 3 else 0.5 for i in range(batch)]
+    a_offs = [i * g["a_stride"] for i in range(batch)]
+    b_offs = [i * g["b_stride"] for i in range(batch)]
+    c_offs = [5 + i * g["c_stride"] for i in range(batch)]
+    da, db, dc = (H.to_device(torch, 32, g[x]) for x in "abc")
+    torch.cuda.synchronize()
+    st = cb.GemmBatched(H.COL, H.NO, H.NO, m, n, k, alphas, da, a_offs, g["a_ld"], db, b_offs, g["b_ld"], betas, dc,
+                        c_offs, g["c_ld"], batch, precision=32)
+    assert st == cb.StatusCode.kSuccess, st
+    assert cb.last_kernel().startswith("tc_f32_3xtf32_narrow"), cb.last_kernel()
+    check(torch, 32, H.COL, H.NO, H.NO, m, n, k, batch, alphas, betas, g, a_offs, b_offs, c_offs, H.to_host(32, dc))
