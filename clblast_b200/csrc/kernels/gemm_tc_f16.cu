@@ -21,9 +21,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
+
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "hgemm_epilogue.cuh"
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -42,7 +45,7 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of BN fp32 columns
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStageBuffers * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 // [0] first timeout code seen (0 = none), [1] block that saw it, [2] role-specific detail.
 __device__ unsigned int g_tc_status[4];
@@ -60,6 +63,7 @@ struct TcParams {
   long long c_stride;
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
+  int c_by_tma;         // C goes out through the staging buffers and TMA stores
 };
 
 // Tiles are walked in groups of `raster_group` m-tiles by all n-tiles, m fastest inside a group, so the CTAs
@@ -78,12 +82,14 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int& tm
 // row per k) instead of one K-major tile (128-byte rows along K).
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES);
+  uint8_t* const staging = base_ptr + STAGES * STAGE_BYTES;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(staging + kStageBuffers * kStageBytes);
   // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) accumulator full, [2S+2,2S+4) accumulator empty
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -107,6 +113,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       mbar_init(acc_full_bar(a), 1);
       mbar_init(acc_empty_bar(a), 4);
     }
+    for (int b = 0; b < kStageBuffers; ++b) mbar_init(bar_base + 192u + 8u * b, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -204,47 +211,56 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else {
     // ---- epilogue: warps 2..5 ----
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+    const int row_in_cta = quad * 32 + lane;
+    const bool elected = threadIdx.x == 64;  // first epilogue thread: issues and tracks the TMA stores
     int local = 0;
+    int stores = 0;
     bool ok = true;
+    HalfEpilogue e;
+    e.ldc = p.ldc; e.m = p.m; e.n = p.n;
+    e.use_tma = p.c_by_tma != 0;
+    e.map_c = &map_c;
+    e.staging = staging;
+    e.load_bars = bar_base + 192u;
+    uint32_t phases = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       int tm, tn;
       const int z = tile / tiles_per_problem;
       tile_coords(p, tile - z * tiles_per_problem, tm, tn);
-      const float alpha = p.alphas ? p.alphas[z] : p.alpha;
-      const float beta = p.betas ? p.betas[z] : p.beta;
-      const bool use_beta = beta != 0.f;
-      __half* const c_base = p.c + z * p.c_stride;
+      e.alpha = p.alphas ? p.alphas[z] : p.alpha;
+      e.beta = p.betas ? p.betas[z] : p.beta;
+      e.c = p.c + z * p.c_stride;
+      e.z = z;
+      const int cta_row0 = tm * BM;
+      const int col0 = tn * BN;
+      // old values only matter where something is stored: CTAs wholly below C skip them
+      const bool use_beta = e.beta != 0.f && cta_row0 < p.m;
+      if (elected && e.use_tma && use_beta) prefetch_first_blocks(e, stores, cta_row0, col0);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_tc_status);
-      ok = __all_sync(0xffffffffu, ok);  // also reconverges the warp before the warp-wide TMEM loads
+      ok = epilogue_all(ok);  // all four warps go on, or none
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = tm * BM + quad * 32 + lane;  // m index of this thread
-      const bool row_ok = row < p.m;
-      const int col0 = tn * BN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; ++cb) {
-        if (col0 + cb * 32 >= p.n) break;  // warp-uniform
+        if (col0 + cb * 32 >= p.n) break;  // uniform over the CTA
         uint32_t r[32];
         tmem_ld_32cols(t_row + cb * 32, r);
-        if (row_ok) {
-          __half* cptr = c_base + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + cb * 32 + j < p.n) {
-              float v = alpha * __uint_as_float(r[j]);
-              if (use_beta) v += beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
-              cptr[static_cast<long long>(j) * p.ldc] = __float2half_rn(v);
-            }
-          }
+        const int ahead = col0 + (cb + 2) * 32;
+        if (!write_block(e, r, cta_row0 + row_in_cta, row_in_cta, cta_row0, col0 + cb * 32,
+                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, g_tc_status)) {
+          ok = false;
+          break;
         }
       }
+      if (!ok) break;
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
     }
+    if (elected) bulk_wait_all();  // shared memory stays valid until the last store has read it
   }
 
   tcgen05_fence_before();
@@ -256,13 +272,13 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 template <bool A_MN, bool B_MN>
-cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid,
-                           cudaStream_t stream) {
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p,
+                           int grid, cudaStream_t stream) {
   auto kernel = hgemm_tc_kernel<A_MN, B_MN>;
   // per-context opt-in to more than 48 KB of dynamic shared memory, repeated per launch (contexts come and go)
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, p);
   return cudaGetLastError();
 }
 
@@ -326,14 +342,17 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
   int sms = sm_count;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  CUtensorMap map_c;
+  p.c_by_tma = encode_half_c_map(&map_c, p.c, d.m, d.n, d.ldc, walk.batches, walk.c_stride) ? 1 : 0;
+  if (!p.c_by_tma) std::memset(&map_c, 0, sizeof(map_c));
   *name = "tc_f16_128x256x64";
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
   if (a_mn) {
-    return b_mn ? launch_variant<true, true>(map_a, map_b, p, grid, stream)
-                : launch_variant<true, false>(map_a, map_b, p, grid, stream);
+    return b_mn ? launch_variant<true, true>(map_a, map_b, map_c, p, grid, stream)
+                : launch_variant<true, false>(map_a, map_b, map_c, p, grid, stream);
   }
-  return b_mn ? launch_variant<false, true>(map_a, map_b, p, grid, stream)
-              : launch_variant<false, false>(map_a, map_b, p, grid, stream);
+  return b_mn ? launch_variant<false, true>(map_a, map_b, map_c, p, grid, stream)
+              : launch_variant<false, false>(map_a, map_b, map_c, p, grid, stream);
 }
 
 }  // namespace b200

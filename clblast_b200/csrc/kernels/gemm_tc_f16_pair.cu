@@ -25,6 +25,7 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "hgemm_epilogue.cuh"
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -44,7 +45,7 @@ constexpr int B_BYTES = BN_HALF * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStageBuffers * kStageBytes + 1024 + 256;
 
 __device__ unsigned int g_pair_status[4];
 
@@ -61,6 +62,7 @@ struct PairParams {
   long long c_stride;
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
+  int c_by_tma;         // C goes out through the staging buffers and TMA stores
 };
 
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& tm, int& tn) {
@@ -76,12 +78,13 @@ __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const PairParams p) {
+                     const __grid_constant__ CUtensorMap map_c, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES);
+  uint8_t* const staging = base_ptr + STAGES * STAGE_BYTES;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(staging + kStageBuffers * kStageBytes);
   const uint32_t bar_base = smem_u32(bars);
   // [0,S) full (used in the leader), [S,2S) empty (each CTA its own), then accumulator full x2 (each CTA its own),
   // accumulator empty x2 (used in the leader)
@@ -110,6 +113,7 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       mbar_init(acc_full_bar(a), 1);
       mbar_init(acc_empty_bar(a), 8);  // four epilogue warps in each of the two CTAs
     }
+    for (int b = 0; b < kStageBuffers; ++b) mbar_init(bar_base + 192u + 8u * b, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -205,47 +209,56 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else {
     // ---- epilogue: warps 2..5 of both CTAs, 128 rows x 256 columns each ----
     const int quad = warp & 3;
+    const int row_in_cta = quad * 32 + lane;
+    const bool elected = threadIdx.x == 64;  // first epilogue thread: issues and tracks the TMA stores
     int local = 0;
+    int stores = 0;
     bool ok = true;
+    HalfEpilogue e;
+    e.ldc = p.ldc; e.m = p.m; e.n = p.n;
+    e.use_tma = p.c_by_tma != 0;
+    e.map_c = &map_c;
+    e.staging = staging;
+    e.load_bars = bar_base + 192u;
+    uint32_t phases = 0;
     for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count, ++local) {
       int tm, tn;
       const int z = tile / tiles_per_problem;
       tile_coords(p, tile - z * tiles_per_problem, tm, tn);
-      const float alpha = p.alphas ? p.alphas[z] : p.alpha;
-      const float beta = p.betas ? p.betas[z] : p.beta;
-      const bool use_beta = beta != 0.f;
-      __half* const c_base = p.c + z * p.c_stride;
+      e.alpha = p.alphas ? p.alphas[z] : p.alpha;
+      e.beta = p.betas ? p.betas[z] : p.beta;
+      e.c = p.c + z * p.c_stride;
+      e.z = z;
+      const int cta_row0 = tm * 2 * BM + static_cast<int>(rank) * BM;
+      const int col0 = tn * BN;
+      // old values only matter where something is stored: CTAs wholly below C skip them
+      const bool use_beta = e.beta != 0.f && cta_row0 < p.m;
+      if (elected && e.use_tma && use_beta) prefetch_first_blocks(e, stores, cta_row0, col0);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_pair_status);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = epilogue_all(ok);  // all four warps go on, or none
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = tm * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
-      const bool row_ok = row < p.m;
-      const int col0 = tn * BN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; ++cb) {
-        if (col0 + cb * 32 >= p.n) break;  // warp-uniform
+        if (col0 + cb * 32 >= p.n) break;  // uniform over the CTA
         uint32_t r[32];
         tmem_ld_32cols(t_row + cb * 32, r);
-        if (row_ok) {
-          __half* cptr = c_base + static_cast<long long>(col0 + cb * 32) * p.ldc + row;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + cb * 32 + j < p.n) {
-              float v = alpha * __uint_as_float(r[j]);
-              if (use_beta) v += beta * __half2float(cptr[static_cast<long long>(j) * p.ldc]);
-              cptr[static_cast<long long>(j) * p.ldc] = __float2half_rn(v);
-            }
-          }
+        const int ahead = col0 + (cb + 2) * 32;
+        if (!write_block(e, r, cta_row0 + row_in_cta, row_in_cta, cta_row0, col0 + cb * 32,
+                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, g_pair_status)) {
+          ok = false;
+          break;
         }
       }
+      if (!ok) break;
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(acc_empty_bar(acc), 0));
     }
+    if (elected) bulk_wait_all();  // shared memory stays valid until the last store has read it
   }
 
   tcgen05_fence_before();
@@ -282,8 +295,8 @@ int resident_pairs() {
 }
 
 template <bool A_MN, bool B_MN>
-cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const PairParams& p, long long tiles,
-                           cudaStream_t stream) {
+cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p,
+                           long long tiles, cudaStream_t stream) {
   auto kernel = hgemm_tc_pair_kernel<A_MN, B_MN>;
   static int pairs_of_device[64] = {0};
   int dev = 0;
@@ -297,7 +310,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
   if (tiles < pairs) pairs = static_cast<int>(tiles);
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
+  kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, p);
   return cudaGetLastError();
 }
 
@@ -360,14 +373,18 @@ cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const cha
   if (!encode_operand_map(&map_b, 2, b, d.n, d.k, d.ldb, !d.b_kcontig, BN_HALF, walk.b_batches, walk.b_stride))
     return cudaErrorNotSupported;
 
+  CUtensorMap map_c;
+  p.c_by_tma = encode_half_c_map(&map_c, p.c, d.m, d.n, d.ldc, walk.batches, walk.c_stride) ? 1 : 0;
+  if (!p.c_by_tma) std::memset(&map_c, 0, sizeof(map_c));
+
   *name = "tc_f16_pair_256x256x64";
   const bool a_mn = !d.a_kcontig, b_mn = !d.b_kcontig;
   if (a_mn) {
-    return b_mn ? launch_variant<true, true>(map_a, map_b, p, tiles, stream)
-                : launch_variant<true, false>(map_a, map_b, p, tiles, stream);
+    return b_mn ? launch_variant<true, true>(map_a, map_b, map_c, p, tiles, stream)
+                : launch_variant<true, false>(map_a, map_b, map_c, p, tiles, stream);
   }
-  return b_mn ? launch_variant<false, true>(map_a, map_b, p, tiles, stream)
-              : launch_variant<false, false>(map_a, map_b, p, tiles, stream);
+  return b_mn ? launch_variant<false, true>(map_a, map_b, map_c, p, tiles, stream)
+              : launch_variant<false, false>(map_a, map_b, map_c, p, tiles, stream);
 }
 
 }  // namespace b200

@@ -313,19 +313,23 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok) break;
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
-      if (!CONV && p.c_rowmajor) {
+      if (BN == 64 && !CONV && p.c_rowmajor) {  // only the 64-column variant is launched on transposed problems
         if (row < p.m) {
           float* cptr = p.c + z * p.gemm_c_stride + static_cast<long long>(row) * p.ldc + col0;
           if (p.c_vec4 && col0 + BN / 2 <= p.n) {
+            float4 old[BN / 8];
+            if (use_beta) {  // all old values first: loads and stores through one pointer would serialise
+#pragma unroll
+              for (int q = 0; q < BN / 8; ++q) old[q] = *reinterpret_cast<const float4*>(cptr + 4 * q);
+            }
 #pragma unroll
             for (int j = 0; j < BN / 2; j += 4) {
               float4 v;
               v.x = __fmul_rn(alpha, acc[j]); v.y = __fmul_rn(alpha, acc[j + 1]);
               v.z = __fmul_rn(alpha, acc[j + 2]); v.w = __fmul_rn(alpha, acc[j + 3]);
               if (use_beta) {
-                const float4 old = *reinterpret_cast<const float4*>(cptr + j);
-                v.x = fmaf(beta, old.x, v.x); v.y = fmaf(beta, old.y, v.y);
-                v.z = fmaf(beta, old.z, v.z); v.w = fmaf(beta, old.w, v.w);
+                v.x = fmaf(beta, old[j / 4].x, v.x); v.y = fmaf(beta, old[j / 4].y, v.y);
+                v.z = fmaf(beta, old[j / 4].z, v.z); v.w = fmaf(beta, old[j / 4].w, v.w);
               }
               *reinterpret_cast<float4*>(cptr + j) = v;
             }
@@ -342,12 +346,24 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       } else if (row < p.m) {
         float* cptr = p.c + (CONV ? image_index * p.c_stride : z * p.gemm_c_stride) + static_cast<long long>(col0) * p.ldc + row;
+        constexpr int G = 8;
+        // G old values are fetched before the first store of a group: loads and stores through one pointer
+        // would otherwise be serialised, one memory latency per element.
 #pragma unroll
-        for (int j = 0; j < BN / 2; ++j) {
-          if (col0 + j < p.n) {
-            float v = __fmul_rn(alpha, acc[j]);
-            if (use_beta) v = fmaf(beta, cptr[static_cast<long long>(j) * p.ldc], v);
-            cptr[static_cast<long long>(j) * p.ldc] = v;
+        for (int j0 = 0; j0 < BN / 2; j0 += G) {
+          float old[G];
+          if (use_beta) {
+#pragma unroll
+            for (int jj = 0; jj < G; ++jj)
+              old[jj] = (col0 + j0 + jj < p.n) ? cptr[static_cast<long long>(j0 + jj) * p.ldc] : 0.f;
+          }
+#pragma unroll
+          for (int jj = 0; jj < G; ++jj) {
+            if (col0 + j0 + jj < p.n) {
+              float v = __fmul_rn(alpha, acc[j0 + jj]);
+              if (use_beta) v = fmaf(beta, old[jj], v);
+              cptr[static_cast<long long>(j0 + jj) * p.ldc] = v;
+            }
           }
         }
       }

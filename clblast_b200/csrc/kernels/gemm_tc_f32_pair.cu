@@ -270,12 +270,23 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int col0 = tn * BN + half * (BN / 2);
       if (row < p.m) {
         float* cptr = p.c + z * p.c_stride + static_cast<long long>(col0) * p.ldc + row;
+        // Eight old values are fetched before the first store of a group: loads and stores through one pointer
+        // would otherwise be serialised, one memory latency per element.
 #pragma unroll
-        for (int j = 0; j < BN / 2; ++j) {
-          if (col0 + j < p.n) {
-            float v = __fmul_rn(alpha, acc[j]);
-            if (use_beta) v = fmaf(beta, cptr[static_cast<long long>(j) * p.ldc], v);
-            cptr[static_cast<long long>(j) * p.ldc] = v;
+        for (int j0 = 0; j0 < BN / 2; j0 += 8) {
+          float old[8];
+          if (use_beta) {
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              old[jj] = (col0 + j0 + jj < p.n) ? cptr[static_cast<long long>(j0 + jj) * p.ldc] : 0.f;
+          }
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            if (col0 + j0 + jj < p.n) {
+              float v = __fmul_rn(alpha, acc[j0 + jj]);
+              if (use_beta) v = fmaf(beta, old[jj], v);
+              cptr[static_cast<long long>(j0 + jj) * p.ldc] = v;
+            }
           }
         }
       }

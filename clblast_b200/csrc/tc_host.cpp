@@ -1,5 +1,7 @@
 #include "tc_host.h"
 
+#include <stdint.h>
+
 #include "driver_api.h"
 
 namespace b200 {
@@ -32,6 +34,24 @@ bool encode_operand_map(CUtensorMap* map, int elem_bytes, const void* base, long
   return drv.TensorMapEncodeTiled(map, type, 3, const_cast<void*>(base), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_half_c_map(CUtensorMap* map, const void* base, long long m, long long n, long long ldc, long long batches,
+                       long long batch_stride) {
+  const DriverApi& drv = driver_api();
+  if (!drv.ok) return false;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return false;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(ldc) * 2;
+  const cuuint64_t batch_bytes = batches > 1 ? static_cast<cuuint64_t>(batch_stride) * 2 : row_bytes;
+  if ((row_bytes & 15) || (batch_bytes & 15) || row_bytes >= (1ULL << 40) || batch_bytes >= (1ULL << 40)) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(n),
+                              static_cast<cuuint64_t>(batches > 1 ? batches : 1)};
+  const cuuint64_t strides[2] = {row_bytes, batch_bytes};
+  const cuuint32_t box[3] = {128, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 BatchWalk batch_walk(const GemmDesc& d) {

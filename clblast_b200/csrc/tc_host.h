@@ -16,6 +16,12 @@ namespace b200 {
 bool encode_operand_map(CUtensorMap* map, int elem_bytes, const void* base, long long rows, long long k, long long ld,
                         bool mn_contig, int kmajor_box_rows, long long batches, long long batch_stride);
 
+// Tensor map for storing a half-precision C (m contiguous): dims {m, n, batches}, box {128 rows, 32 columns, 1}, no
+// swizzle (the staging buffer holds 32 columns of 128 contiguous rows). False when C is not 16-byte aligned or its
+// leading dimension / batch stride is not a multiple of 8 elements: the caller then stores with plain instructions.
+bool encode_half_c_map(CUtensorMap* map, const void* base, long long m, long long n, long long ldc, long long batches,
+                       long long batch_stride);
+
 // How a launcher walks the batch of a strided call (or of an offset-table call whose offsets are evenly spaced).
 struct BatchWalk {
   bool ok;              // false: the descriptor's batch cannot be expressed with strides
