@@ -31,20 +31,6 @@ constexpr int kStageCols = 32;                                   // columns per 
 constexpr int kStageBytes = kStageRows * kStageCols * 2;         // 8 KB
 constexpr int kStageBuffers = 4;
 
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(src), "r"(x), "r"(y), "r"(z)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until all but the newest `N` bulk groups of this thread have finished READING shared memory.
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-// Waits until every bulk group of this thread has completed.
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Barrier among the 128 epilogue threads only (barrier 0 belongs to __syncthreads).
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -83,23 +69,6 @@ __device__ __forceinline__ void prefetch_old_block(const HalfEpilogue& e, int bl
   const uint32_t bar = e.load_bars + 8u * b;
   mbar_arrive_expect_tx(bar, kStageBytes);
   tma_load_3d(smem_u32(e.staging + b * kStageBytes), e.map_c, bar, cta_row0, col, e.z);
-}
-
-// Wait for an old-C block. Not tied to the CTA's abort flag: the load completes whatever the other roles do, and
-// all 128 threads wait on the same barrier, so they give up (after the same bounded time) together or not at all.
-__device__ __forceinline__ bool wait_old_block(uint32_t bar, uint32_t parity, unsigned int* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > kWaitCycles) {
-      if (atomicCAS(&status[0], 0u, 6u) == 0u) {
-        status[1] = blockIdx.x;
-        status[2] = bar;
-      }
-      return false;
-    }
-  }
-  return true;
 }
 
 // Start of a tile on the TMA path with beta != 0 (elected thread only): requests the old values of the tile's first

@@ -161,6 +161,39 @@ __device__ __forceinline__ float to_tf32(float x) {
 }
 
 
+// ---- results leaving through shared memory and TMA stores ---------------------------------------------------------
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until all but the newest `N` bulk groups of this thread have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until every bulk group of this thread has completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Wait for a block of old C values requested by a TMA load. Not tied to the CTA's abort flag: the load completes whatever the other roles do, and
+// all 128 threads wait on the same barrier, so they give up (after the same bounded time) together or not at all.
+__device__ __forceinline__ bool wait_old_block(uint32_t bar, uint32_t parity, unsigned int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > kWaitCycles) {
+      if (atomicCAS(&status[0], 0u, 6u) == 0u) {
+        status[1] = blockIdx.x;
+        status[2] = bar;
+      }
+      return false;
+    }
+  }
+  return true;
+}
+
 // ---- CTA pairs (clusters of two, tcgen05 cta_group::2) -------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
