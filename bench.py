@@ -597,7 +597,7 @@ def main():
     if args.workload == "hgemm_8192":
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
         # profiles/hgemm_tc_pair_kernel__hgemm_8192.md
-        roof["traffic"] = 1.228e9
+        roof["traffic"] = 1.22e9
 
     if rank == 0 and n_gpus == 1 and not args.no_sweep:
         sweep = {}
