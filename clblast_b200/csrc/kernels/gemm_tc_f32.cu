@@ -154,7 +154,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(raw_full(s), 1);
-      mbar_init(split_full(s), 8);
+      mbar_init(split_full(s), MODE == kTma ? 4 : 8);  // arrivals: one per warp of the group that splits the stage
       mbar_init(stage_free(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -375,6 +375,38 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    if constexpr (MODE == kTma) {
+      // Two groups of four warps take alternate K blocks, so the wait / fence / arrive latency of one stage
+      // overlaps the conversion work of the next.
+      const int group = t >> 7, gt = t & 127;
+      constexpr int CHUNKS_ALL = (C::A_BYTES + C::B_BYTES) / 16;
+      int kbg = 0;  // running K-block count of this CTA
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++kbg) {
+          if ((kbg & 1) != group) continue;
+          const int st = kbg % STAGES;
+          const uint32_t ph = static_cast<uint32_t>(kbg / STAGES) & 1u;
+          ok = mbar_wait(raw_full(st), ph, abort_flag, 5u, g_tc32_status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + st * C::STAGE_BYTES);
+          float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + st * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+#pragma unroll 4
+          for (int c = gt; c < CHUNKS_ALL; c += 128) {
+            const float4 x = main_ptr[c];
+            float4 hi, lo;
+            hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
+            lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z);
+            lo.w = to_tf32(x.w - hi.w);
+            main_ptr[c] = hi;
+            lo_ptr[c] = lo;
+          }
+          fence_proxy_async();  // the tensor cores read these tiles through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(split_full(st));
+        }
+      }
+    } else {
     // GEMM: A and B main tiles are adjacent, so are the lo tiles, and all are split. Convolution: only B is split
     // from its raw copy; A is produced below.
     constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;
@@ -530,6 +562,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
+    }  // gathered / convolution variants
   }
 
   tcgen05_fence_before();
