@@ -108,7 +108,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(raw_full(s), 1);
-      mbar_init(split_full(s), 16);  // eight split warps in each of the two CTAs
+      mbar_init(split_full(s), 8);   // the four warps of one split group in each of the two CTAs
       mbar_init(stage_free(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -294,20 +294,25 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SPLIT_REGS));
     // ---- split: warps 4..11 turn this CTA's raw fp32 tiles into TF32 big parts (in place) and small parts ----
+    // Two groups of four warps take alternate K blocks, so the wait / fence / arrive latency of one stage overlaps
+    // the conversion work of the next.
     const int t = threadIdx.x - 4 * 32;
-    int stage = 0;
-    uint32_t phase = 0;
+    const int group = t >> 7, gt = t & 127;
     bool ok = true;
     constexpr int CHUNKS = (A_BYTES + B_BYTES) / 16;
+    int kbg = 0;  // running K-block count of this CTA
     for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count) {
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++kbg) {
+        if ((kbg & 1) != group) continue;
+        const int stage = kbg % STAGES;
+        const uint32_t phase = static_cast<uint32_t>(kbg / STAGES) & 1u;
         ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_pair_status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * STAGE_BYTES);
         float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + stage * STAGE_BYTES + A_BYTES + B_BYTES);
 #pragma unroll 4
-        for (int c = t; c < CHUNKS; c += 256) {
+        for (int c = gt; c < CHUNKS; c += 128) {
           const float4 x = main_ptr[c];
           float4 hi, lo;
           hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
@@ -318,7 +323,6 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         fence_proxy_async();  // the tensor cores of both SMs read these tiles through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(map_to_cta(split_full(stage), 0));
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   }
