@@ -43,10 +43,18 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
   const bool a_vec_ok = (p.lda % 2) == 0, b_vec_ok = (p.ldb % 2) == 0;
 
   for (long long tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-    const long long tm = tile % p.tiles_m;
-    const long long rest = tile / p.tiles_m;
-    const long long tn = rest % p.tiles_n;
-    const long long bz = rest / p.tiles_n;
+    // Tiles are walked in groups of eight tile rows by all tile columns (rows fastest inside a group), so the CTAs
+    // running at the same time share a few operand rows and columns in L2 instead of sweeping all of A.
+    const long long per_problem = p.tiles_m * p.tiles_n;
+    const long long bz = tile / per_problem;
+    const long long in_problem = tile - bz * per_problem;
+    const long long per_group = 8 * p.tiles_n;
+    const long long group = in_problem / per_group;
+    const long long first_m = group * 8;
+    const long long rows = (p.tiles_m - first_m) < 8 ? (p.tiles_m - first_m) : 8;
+    const long long in_group = in_problem - group * per_group;
+    const long long tm = first_m + in_group % rows;
+    const long long tn = in_group / rows;
     const long long m0 = tm * BM, n0 = tn * BN;
     const long long m_rem = p.m - m0, n_rem = p.n - n0;
     const double* a_base = static_cast<const double*>(p.a) + (p.a_offs ? p.a_offs[bz] : p.a_off + bz * p.a_stride);
@@ -92,10 +100,15 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
             asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
                          : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
                          : "d"(af[i]), "d"(bf[j]));
+        // The next K block goes to the other buffer half-way through this one: nobody reads that buffer any more
+        // (everyone passed the barrier below after its last use), and the stores, bank conflicts of the transposing
+        // ones included, run under the remaining DMMAs instead of leaving the FP64 pipe idle.
+        if (ks == BK / 2 - 4 && has_next) {
+          StA::template stash<LDS_A>(sA[cur ^ 1], ra, false, tid);
+          StB::template stash<LDS_B>(sB[cur ^ 1], rb, false, tid);
+        }
       }
       if (has_next) {
-        StA::template stash<LDS_A>(sA[cur ^ 1], ra, false, tid);
-        StB::template stash<LDS_B>(sB[cur ^ 1], rb, false, tid);
         __syncthreads();
         cur ^= 1;
       }
