@@ -578,7 +578,9 @@ def main():
 
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": n_gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        # one problem split over the ranks keeps the total work fixed; every other workload is one copy per rank
+        "scaling": "strong" if w["kind"] == "sharded" else "weak",
         "vs_baseline": None, "dtype": {16: "f16", 32: "f32", 64: "f64"}[w["precision"]], "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in w.items() if k not in ("kind", "bound")},
                    "per_gpu": "one full copy of the workload per GPU; B re-broadcast from rank 0 every step, overlapped with the previous step's GEMM" if n_gpus > 1
