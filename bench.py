@@ -411,7 +411,8 @@ def main():
         torch.cuda.synchronize()
         t["b"] = bcast["bufs"][0]
 
-    total_flops = flops_of(w) * n_gpus
+    # a sharded workload is ONE problem split over the ranks; every other workload is one full copy per rank
+    total_flops = flops_of(w) * (1 if w["kind"] == "sharded" else n_gpus)
     ms_per_step = ms / args.steps
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
