@@ -452,7 +452,9 @@ def main():
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "peak_source": f"{peak_kind} STREAM-style copy"}
     else:
-        achieved = flops_of(w) / (kms * 1e-3) / 1e12
+        # the kernel of a sharded workload computes this rank's column block only
+        kernel_flops = flops_of(w) * (t["n_local"] / w["n"] if w["kind"] == "sharded" else 1)
+        achieved = kernel_flops / (kms * 1e-3) / 1e12
         if bound == "tensor":
             peak = float(peaks["bf16_tflops"])
             src = f"{peak_kind} cuBLAS bf16 burst"
