@@ -49,7 +49,7 @@ constexpr int NUM_THREADS = 640;
 // increase waits forever: 128 producer threads x 40 + 256 split threads x 56 + 256 drain threads x 160.
 constexpr int LAUNCH_REGS = 96;  // floor(65536 / 640) rounded down to the allocation granularity of 8
 static_assert(128 * 40 + 256 * 56 + 256 * 160 <= NUM_THREADS * LAUNCH_REGS, "register budgets exceed the CTA's pool");
-constexpr int CHUNK_KB = 2;  // K blocks accumulated inside the tensor cores before a partial is drained
+constexpr int CHUNK_KB = 4;  // K blocks accumulated inside the tensor cores before a partial is drained
 constexpr int TMEM_COLS = 512;
 
 __device__ unsigned int g_tc32_status[4];
