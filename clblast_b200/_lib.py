@@ -48,6 +48,21 @@ def lib() -> ctypes.CDLL:
     L.b200blas_retrieve_parameters.argtypes = [i, c_char_p, i, POINTER(c_char_p), POINTER(sz), sz, POINTER(sz)]
     L.b200blas_set_sm_budget.restype = None
     L.b200blas_set_sm_budget.argtypes = [i]
+    u8p = POINTER(ctypes.c_ubyte)
+    L.b200blas_ipc_export.restype = i
+    L.b200blas_ipc_export.argtypes = [vp, u8p, POINTER(sz)]
+    L.b200blas_ipc_open.restype = i
+    L.b200blas_ipc_open.argtypes = [u8p, sz, POINTER(vp)]
+    L.b200blas_ipc_close.restype = i
+    L.b200blas_ipc_close.argtypes = [vp, sz]
+    L.b200blas_stream_copy.restype = i
+    L.b200blas_stream_copy.argtypes = [vp, vp, vp, sz]
+    L.b200blas_stream_wait_flag.restype = i
+    L.b200blas_stream_wait_flag.argtypes = [vp, vp, ctypes.c_uint32]
+    L.b200blas_stream_write_flag.restype = i
+    L.b200blas_stream_write_flag.argtypes = [vp, vp, ctypes.c_uint32]
+    L.b200blas_tensor_core_status.restype = i
+    L.b200blas_tensor_core_status.argtypes = [POINTER(ctypes.c_uint), i]
     L.b200blas_last_kernel.restype = c_char_p
     L.b200blas_last_kernel.argtypes = []
     L.b200blas_launch_count.restype = c_uint64
@@ -63,5 +78,6 @@ C_ABI_SYMBOLS = [
     "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_gemm_batched_static",
     "b200blas_convgemm",
     "b200blas_gemm_temp_buffer_size", "b200blas_clear_cache", "b200blas_fill_cache", "b200blas_override_parameters",
-    "b200blas_retrieve_parameters", "b200blas_set_sm_budget", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
+    "b200blas_retrieve_parameters", "b200blas_set_sm_budget", "b200blas_tensor_core_status", "b200blas_ipc_export", "b200blas_ipc_open",
+    "b200blas_ipc_close", "b200blas_stream_copy", "b200blas_stream_wait_flag", "b200blas_stream_write_flag", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
 ]

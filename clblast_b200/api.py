@@ -248,6 +248,14 @@ def set_sm_budget(sms: int) -> None:
     lib().b200blas_set_sm_budget(int(sms))
 
 
+def tensor_core_status(clear: bool = True):
+    """(status, [code, block, barrier, 0]) of the tensor-core kernels' bounded waits; for callers that enqueue on their
+    own stream, after synchronising it. status is kUnexpectedError when a wait expired since the last clear."""
+    out = (ctypes.c_uint * 4)()
+    st = lib().b200blas_tensor_core_status(out, 1 if clear else 0)
+    return _status(st), list(out)
+
+
 def last_kernel() -> str:
     """Kernel family chosen by the most recent compute call on this thread."""
     return lib().b200blas_last_kernel().decode()

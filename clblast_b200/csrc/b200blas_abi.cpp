@@ -23,6 +23,7 @@
 #include "kernels/launchers.h"
 #include "noalloc_bridge.h"
 #include "params_store.h"
+#include "runtime_state.h"
 
 namespace b200 {
 
@@ -45,6 +46,10 @@ enum Status : int {
   kInvalidBatchCount = -2049,
   kUnexpectedError = -2039,
 };
+
+// Upper bound on batch_count of the offset-table form: the staged tables take 56 bytes per batch, so this is 3.5 GB
+// of tables; anything larger is a corrupt argument rather than a workload.
+constexpr size_t kMaxBatchCount = size_t(1) << 26;
 
 constexpr int kRowMajor = 101, kColMajor = 102;
 constexpr int kNo = 111, kYes = 112, kConjugate = 113;
@@ -192,22 +197,9 @@ std::map<unsigned long long, cudaStream_t> g_streams;
 
 // The library-owned non-blocking stream of the current context (one per context, created on first use).
 int private_stream(cudaStream_t* out) {
-  const DriverApi& drv = driver_api();
-  if (!drv.ok) return CUDA_ERROR_NOT_INITIALIZED;
-  CUcontext ctx = nullptr;
-  CUresult r = drv.CtxGetCurrent(&ctx);
-  if (r != CUDA_SUCCESS) return static_cast<int>(r);
-  if (!ctx) {
-    // No context is current: let the runtime bind the primary context of the current device.
-    if (cudaFree(nullptr) != cudaSuccess) return static_cast<int>(cudaGetLastError());
-    r = drv.CtxGetCurrent(&ctx);
-    if (r != CUDA_SUCCESS || !ctx) return CUDA_ERROR_INVALID_CONTEXT;
-  }
-  unsigned long long key = reinterpret_cast<unsigned long long>(ctx);
-  if (drv.CtxGetId) {
-    unsigned long long id = 0;
-    if (drv.CtxGetId(ctx, &id) == CUDA_SUCCESS) key = (id << 1) | 1ull;  // odd keys: ids; even keys: handle values
-  }
+  unsigned long long key = 0;
+  const int r = context_key(&key);
+  if (r != 0) return r;
   std::lock_guard<std::mutex> lock(g_stream_mutex);
   auto it = g_streams.find(key);
   if (it == g_streams.end()) {
@@ -275,19 +267,13 @@ int run(const GemmDesc& d, void* stream, int async) {
   return tensor_core_status(async);
 }
 
-// After a synchronous call that ran a tensor-core kernel: the kernel reports expired waits through a status word
-// instead of hanging or trapping.
+// After a synchronous call that ran a tensor-core kernel: the kernel reports expired waits through the status block
+// (mapped host memory, so this is a plain read after the stream synchronisation the call has just done) instead of
+// hanging or trapping. Asynchronous callers read it with b200blas_tensor_core_status once their stream has finished.
 int tensor_core_status(int async) {
   if (!async && std::strncmp(t_last_kernel, "tc_", 3) == 0) {
     unsigned int status[4] = {0, 0, 0, 0};
-    const bool is_f32 = std::strncmp(t_last_kernel, "tc_f32", 6) == 0 || std::strncmp(t_last_kernel, "tc_conv", 7) == 0;
-    const bool is_pair = std::strncmp(t_last_kernel, "tc_f16_pair", 11) == 0;
-    const bool is_f32_pair = std::strncmp(t_last_kernel, "tc_f32_3xtf32_pair", 18) == 0;
-    const cudaError_t serr = is_f32_pair ? tc_f32_pair_status(status, true)
-                             : is_f32    ? tc_f32_status(status, true)
-                             : is_pair   ? tc_f16_pair_status(status, true)
-                                         : tc_f16_status(status, true);
-    if (serr == cudaSuccess && status[0] != 0) {
+    if (tc_status_read(status, true) && status[0] != 0) {
       std::fprintf(stderr, "b200blas: tensor-core kernel gave up waiting (code %u, block %u)\n", status[0], status[1]);
       return kUnexpectedError;
     }
@@ -411,6 +397,8 @@ void patch_batched_tables(GemmDesc* d, const BatchedTables& t, const unsigned ch
 
 cudaError_t dispatch_desc(const GemmDesc& d, cudaStream_t stream) { return dispatch(d, stream); }
 
+int status_after_sync() { return tensor_core_status(0); }
+
 }  // namespace b200
 
 using namespace b200;
@@ -493,7 +481,14 @@ extern "C" int b200blas_gemm_batched(int dtype, int layout, int ta, int tb, size
   // Argument checks, normalisation and the per-batch tables (three offset tables, then alphas and betas converted
   // to the kernel's compute type) are shared with the allocation-free entry point. As in the reference, the
   // leading dimensions of A and B are deliberately not tested for this routine.
-  std::vector<unsigned char> host(3 * sizeof(long long) * batch_count + 16 + 2 * (16 * batch_count + 16));
+  if (batch_count < 1 || batch_count > kMaxBatchCount || !alphas || !betas || !a_offsets || !b_offsets || !c_offsets)
+    return kInvalidBatchCount;
+  std::vector<unsigned char> host;
+  try {
+    host.resize(3 * sizeof(long long) * batch_count + 16 + 2 * (16 * batch_count + 16));
+  } catch (...) {
+    return kUnexpectedError;
+  }
   GemmDesc d = {};
   BatchedTables tables = {};
   const int st = prepare_batched(dtype, layout, ta, tb, m, n, k, alphas, a, a_offsets, a_ld, b, b_offsets, b_ld, betas,
@@ -610,6 +605,13 @@ extern "C" void b200blas_set_sm_budget(int sms) { g_sm_budget.store(sms > 0 ? sm
 
 extern "C" int b200blas_clear_cache(void) { return kSuccess; }
 extern "C" int b200blas_fill_cache(int) { return kSuccess; }
+
+extern "C" int b200blas_tensor_core_status(unsigned int out[4], int clear) {
+  unsigned int status[4] = {0, 0, 0, 0};
+  if (!tc_status_read(status, clear != 0)) return kUnexpectedError;
+  if (out) std::memcpy(out, status, sizeof(status));
+  return status[0] != 0 ? kUnexpectedError : kSuccess;
+}
 
 extern "C" const char* b200blas_last_kernel(void) { return t_last_kernel; }
 extern "C" uint64_t b200blas_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -17,6 +17,8 @@ DriverApi bind() {
   api.CtxGetId = reinterpret_cast<decltype(api.CtxGetId)>(sym("cuCtxGetId"));
   api.MemGetAddressRange = reinterpret_cast<decltype(api.MemGetAddressRange)>(sym("cuMemGetAddressRange_v2"));
   api.TensorMapEncodeTiled = reinterpret_cast<decltype(api.TensorMapEncodeTiled)>(sym("cuTensorMapEncodeTiled"));
+  api.StreamWaitValue32 = reinterpret_cast<decltype(api.StreamWaitValue32)>(sym("cuStreamWaitValue32_v2"));
+  api.StreamWriteValue32 = reinterpret_cast<decltype(api.StreamWriteValue32)>(sym("cuStreamWriteValue32_v2"));
   api.ok = api.CtxGetCurrent && api.CtxPushCurrent && api.CtxPopCurrent && api.MemGetAddressRange &&
            api.TensorMapEncodeTiled;
   return api;

@@ -13,15 +13,20 @@
 //   - all calls on a device share the array, and it keeps the previous call's tables: a call overwrites the part
 //     it uses before its kernel starts, in stream order. Two calls whose work overlaps on the GPU (different
 //     streams, or two host threads) race on it; callers must order them themselves;
-//   - the first call on each device resolves the array's device address; make that call before starting any
-//     stream capture.
+//   - the first call under each context resolves the array's device address in that context;
+//   - the call is refused (kUnexpectedError, nothing enqueued) on a stream that is being captured: the host block
+//     its table copy reads is reused by the next call.
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <map>
+#include <memory>
 #include <mutex>
+#include <new>
 
 #include "b200blas.h"
 #include "noalloc_bridge.h"
+#include "runtime_state.h"
 
 namespace b200 {
 
@@ -32,29 +37,38 @@ constexpr size_t kMaxBatches = B200BLAS_STATIC_MAX_BATCHES;
 constexpr size_t kTableBytes = kMaxBatches * (3 * 8 + 2 * 16) + 64;
 
 // In host code this name is only a handle for the symbol, never a device address; the address is resolved once
-// per device with cudaGetSymbolAddress below and that pointer is what kernels receive.
+// per context with cudaGetSymbolAddress below and that pointer is what kernels receive.
 static __device__ __align__(256) unsigned char g_batched_tables[kTableBytes];
 
-constexpr int kMaxDevices = 64;
+// The symbol's address belongs to a context, not to a device ordinal: a process that drives one GPU through several
+// contexts (CLBlast callers pass contexts made with cuCtxCreate) gets one copy of the array per context. Addresses
+// are therefore cached under the same context key the library's private streams use.
 std::mutex g_setup_mutex;
-unsigned char* g_table_address[kMaxDevices] = {nullptr};
+std::map<unsigned long long, unsigned char*> g_table_address;
 
-// Device address of the table on the current device, resolved on first use with that device current.
+// Device address of the table in the current context, resolved on the first call made under that context.
 cudaError_t table_address(unsigned char** out) {
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  unsigned long long key = 0;
+  if (context_key(&key) != 0) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lock(g_setup_mutex);
-  if (g_table_address[dev] == nullptr) {
+  auto it = g_table_address.find(key);
+  if (it == g_table_address.end()) {
     unsigned char* ptr = nullptr;
-    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_batched_tables);
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_batched_tables);
     if (err != cudaSuccess) return err;
     if (ptr == nullptr) return cudaErrorInvalidSymbol;
-    g_table_address[dev] = ptr;
+    it = g_table_address.emplace(key, ptr).first;
   }
-  *out = g_table_address[dev];
+  *out = it->second;
   return cudaSuccess;
+}
+
+// Host staging block of the calling thread (host memory, kept for the thread's lifetime): the tables are far too
+// large for the small stacks of worker threads that language runtimes create.
+unsigned char* host_staging() {
+  thread_local std::unique_ptr<unsigned char[]> block;
+  if (!block) block.reset(new (std::nothrow) unsigned char[kTableBytes]);
+  return block.get();
 }
 
 }  // namespace
@@ -72,19 +86,28 @@ extern "C" int b200blas_gemm_batched_static(int dtype, int layout, int a_transpo
                  batch_count, kMaxBatches);
     return -2049;  // kInvalidBatchCount
   }
-  // Host staging lives on this thread's stack; the copy below is from pageable memory, so it has been consumed
-  // by the time cudaMemcpyAsync returns.
-  alignas(16) unsigned char host_block[kTableBytes];
+  // A capturing stream is refused before anything is enqueued: the table copy below reads a host block that is
+  // rewritten by the next call, so a graph holding that copy would replay stale tables.
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    std::fprintf(stderr, "b200blas_gemm_batched_static: the stream is being captured; the call is refused\n");
+    return -2039;  // kUnexpectedError
+  }
+  // The copy below is from pageable memory, so the block has been consumed by the time cudaMemcpyAsync returns
+  // and the thread's next call may overwrite it.
+  unsigned char* const host_block = host_staging();
+  if (host_block == nullptr) return -2039;
   GemmDesc desc;
   BatchedTables tables;
   const int status = prepare_batched(dtype, layout, a_transpose, b_transpose, m, n, k, alphas, a, a_offsets, a_ld, b,
-                                     b_offsets, b_ld, betas, c, c_offsets, c_ld, batch_count, host_block,
-                                     sizeof(host_block), &desc, &tables);
+                                     b_offsets, b_ld, betas, c, c_offsets, c_ld, batch_count, host_block, kTableBytes,
+                                     &desc, &tables);
   if (status != 0) return status;
 
   unsigned char* device_block = nullptr;
   cudaError_t err = table_address(&device_block);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (err == cudaSuccess) err = cudaMemcpyAsync(device_block, host_block, tables.total, cudaMemcpyHostToDevice, s);
   if (err == cudaSuccess) {
     patch_batched_tables(&desc, tables, device_block);
@@ -96,5 +119,6 @@ extern "C" int b200blas_gemm_batched_static(int dtype, int layout, int a_transpo
                  cudaGetErrorString(err));
     return static_cast<int>(err);
   }
-  return 0;
+  // With `wait` the stream has finished: report a tensor-core kernel whose bounded wait expired.
+  return wait ? status_after_sync() : 0;
 }

@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include "launchers.h"
+#include "../runtime_state.h"
 
 namespace b200 {
 
@@ -328,20 +329,17 @@ cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, con
   p.batch = d.batch;
   p.need_c = (d.betas != nullptr) || (p.beta != 0.f);
 
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  const int device_sms = sm_count();
+  if (device_sms <= 0) return cudaErrorNotSupported;
 
   // Thread tiles of 4 x 4 (8 x 4 for the wide class) keep several warps per scheduler busy: with 8 x 8 tiles a
   // scheduler had a single warp and issued at 0.42 instructions per cycle.
   if (fits_small) {
     *name = "small_batched_f32_32x32x32";
-    return SmallLauncher<32, 32, 32, 4, 4, 1, 2, 8>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
+    return SmallLauncher<32, 32, 32, 4, 4, 1, 2, 8>::launch(p, d.a_kcontig, d.b_kcontig, stream, device_sms);
   }
   *name = "small_batched_f32_64x128x96";
-  return SmallLauncher<64, 128, 96, 8, 4, 1, 1>::launch(p, d.a_kcontig, d.b_kcontig, stream, sm_counts[dev]);
+  return SmallLauncher<64, 128, 96, 8, 4, 1, 1>::launch(p, d.a_kcontig, d.b_kcontig, stream, device_sms);
 }
 
 }  // namespace b200

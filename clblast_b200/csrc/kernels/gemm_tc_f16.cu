@@ -14,7 +14,7 @@
 //
 // Roles per CTA (192 threads): warp 0 lane 0 issues TMA loads; warp 1 owns TMEM and lane 0 issues the MMAs;
 // warps 2-5 drain accumulators (each warp reads the 32 TMEM lanes its rank modulo 4 may access).
-// Every wait is bounded: on expiry the CTA records a code in g_tc_status, all roles leave their loops, copies
+// Every wait is bounded: on expiry the CTA records a code in the status block, all roles leave their loops, copies
 // already in flight are waited for (bounded again), TMEM is released and the kernel returns.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -26,6 +26,7 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "../runtime_state.h"
 #include "hgemm_epilogue.cuh"
 #include "tc_common.cuh"
 
@@ -48,9 +49,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStageBuffers * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 // [0] first timeout code seen (0 = none), [1] block that saw it, [2] role-specific detail.
-__device__ unsigned int g_tc_status[4];
-
 struct TcParams {
+  unsigned int* status;  // where an expired bounded wait is reported (mapped host memory), or null
   __half* c;
   long long ldc;
   int m, n, k;          // normalised extents: C is m x n with m contiguous
@@ -138,7 +138,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tile_coords(p, tile - z * tiles_per_problem, tm, tn);
         const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, g_tc_status)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_BYTES;
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -184,11 +184,11 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u, g_tc_status)) { ok = false; break; }
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u, p.status)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u, g_tc_status)) { ok = false; break; }
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u, p.status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_BYTES;
@@ -238,7 +238,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (elected && e.use_tma && use_beta) prefetch_first_blocks(e, stores, cta_row0, col0);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_tc_status);
+      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, p.status);
       ok = epilogue_all(ok);  // all four warps go on, or none
       if (!ok) break;
       tcgen05_fence_after();
@@ -250,7 +250,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tmem_ld_32cols(t_row + cb * 32, r);
         const int ahead = col0 + (cb + 2) * 32;
         if (!write_block(e, r, cta_row0 + row_in_cta, row_in_cta, cta_row0, col0 + cb * 32,
-                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, g_tc_status)) {
+                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, p.status)) {
           ok = false;
           break;
         }
@@ -284,15 +284,6 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const C
 
 }  // namespace
 
-cudaError_t tc_f16_status(unsigned int out[4], bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_status, sizeof(unsigned int) * 4);
-  if (e == cudaSuccess && clear && out[0] != 0) {
-    const unsigned int zero[4] = {0, 0, 0, 0};
-    e = cudaMemcpyToSymbol(g_tc_status, zero, sizeof(zero));
-  }
-  return e;
-}
-
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
@@ -311,6 +302,7 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
     return cudaErrorNotSupported;
 
   TcParams p;
+  p.status = tc_status_device();
   p.batches = walk.batches;
   p.a_batched = walk.a_batches > 1;
   p.b_batched = walk.b_batches > 1;
@@ -331,15 +323,11 @@ cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** n
 
   // SM count is cached per device; the opt-in to more than 48 KB of dynamic shared memory is per context, and
   // contexts come and go, so it is simply repeated before every launch (a host-side attribute write).
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  const int sm_count = sm_counts[dev];
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
+  const int device_sms = sm_count();
+  if (device_sms <= 0) return cudaErrorNotSupported;
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
-  int sms = sm_count;
+  int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   CUtensorMap map_c;

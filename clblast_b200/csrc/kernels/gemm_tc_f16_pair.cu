@@ -25,6 +25,7 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "../runtime_state.h"
 #include "hgemm_epilogue.cuh"
 #include "tc_common.cuh"
 
@@ -47,9 +48,8 @@ constexpr int TMEM_COLS = 512;  // two accumulators of 256 fp32 columns
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + kStageBuffers * kStageBytes + 1024 + 256;
 
-__device__ unsigned int g_pair_status[4];
-
 struct PairParams {
+  unsigned int* status;  // where an expired bounded wait is reported (mapped host memory), or null
   __half* c;
   long long ldc;
   int m, n, k;
@@ -63,6 +63,7 @@ struct PairParams {
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
   int c_by_tma;         // C goes out through the staging buffers and TMA stores
+  int hint_a, hint_b;   // L2 eviction priority of the operand loads (0 normal, 1 evict-first, 2 evict-last)
 };
 
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& tm, int& tn) {
@@ -135,6 +136,7 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
       for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count) {
         int tm, tn;
         const int z = tile / tiles_per_problem;
@@ -143,7 +145,7 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int b_row0 = tn * BN + static_cast<int>(rank) * BN_HALF;
         const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, g_pair_status)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_dst = a_dst + A_BYTES;
           const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
@@ -151,16 +153,16 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_3d_pair(a_dst + j * 8192, &map_a, lead_full, a_row0 + j * 64, kb * BK, az);
+              tma_load_3d_pair_hint(a_dst + j * 8192, &map_a, lead_full, a_row0 + j * 64, kb * BK, az, pol_a);
           } else {
-            tma_load_3d_pair(a_dst, &map_a, lead_full, kb * BK, a_row0, az);
+            tma_load_3d_pair_hint(a_dst, &map_a, lead_full, kb * BK, a_row0, az, pol_a);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN_HALF / 64; ++j)
-              tma_load_3d_pair(b_dst + j * 8192, &map_b, lead_full, b_row0 + j * 64, kb * BK, bz);
+              tma_load_3d_pair_hint(b_dst + j * 8192, &map_b, lead_full, b_row0 + j * 64, kb * BK, bz, pol_b);
           } else {
-            tma_load_3d_pair(b_dst, &map_b, lead_full, kb * BK, b_row0, bz);
+            tma_load_3d_pair_hint(b_dst, &map_b, lead_full, kb * BK, b_row0, bz, pol_b);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -183,11 +185,11 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (int tile = pair_index; tile < num_tiles && ok; tile += pair_count, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u, g_pair_status)) { ok = false; break; }
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, 2u, p.status)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u, g_pair_status)) { ok = false; break; }
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, 3u, p.status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_BYTES;
@@ -236,7 +238,7 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (elected && e.use_tma && use_beta) prefetch_first_blocks(e, stores, cta_row0, col0);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, g_pair_status);
+      ok = mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, 4u, p.status);
       ok = epilogue_all(ok);  // all four warps go on, or none
       if (!ok) break;
       tcgen05_fence_after();
@@ -248,7 +250,7 @@ hgemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tmem_ld_32cols(t_row + cb * 32, r);
         const int ahead = col0 + (cb + 2) * 32;
         if (!write_block(e, r, cta_row0 + row_in_cta, row_in_cta, cta_row0, col0 + cb * 32,
-                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, g_pair_status)) {
+                         (cb + 2 < BN / 32 && ahead < p.n) ? ahead : -1, use_beta, stores, phases, elected, p.status)) {
           ok = false;
           break;
         }
@@ -276,7 +278,7 @@ int resident_pairs() {
   auto kernel = hgemm_tc_pair_kernel<A_MN, B_MN>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.gridDim = dim3(2 * sm_count(), 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cudaLaunchAttribute attr[1];
@@ -298,12 +300,8 @@ template <bool A_MN, bool B_MN>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const PairParams& p,
                            long long tiles, cudaStream_t stream) {
   auto kernel = hgemm_tc_pair_kernel<A_MN, B_MN>;
-  static int pairs_of_device[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (pairs_of_device[dev] == 0) pairs_of_device[dev] = resident_pairs<A_MN, B_MN>();
-  int pairs = pairs_of_device[dev];
+  static std::atomic<int> pairs_of_device[kMaxDevices];
+  int pairs = per_device(pairs_of_device, &resident_pairs<A_MN, B_MN>);
   if (pairs <= 0) return cudaErrorNotSupported;
   if (sm_budget() > 0 && sm_budget() / 2 < pairs) pairs = sm_budget() / 2;
   if (pairs <= 0) return cudaErrorNotSupported;
@@ -315,15 +313,6 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const C
 }
 
 }  // namespace
-
-cudaError_t tc_f16_pair_status(unsigned int out[4], bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_pair_status, sizeof(unsigned int) * 4);
-  if (e == cudaSuccess && clear && out[0] != 0) {
-    const unsigned int zero[4] = {0, 0, 0, 0};
-    e = cudaMemcpyToSymbol(g_pair_status, zero, sizeof(zero));
-  }
-  return e;
-}
 
 cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
@@ -343,6 +332,7 @@ cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const cha
   if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorNotSupported;
 
   PairParams p;
+  p.status = tc_status_device();
   p.batches = walk.batches;
   p.a_batched = walk.a_batches > 1;
   p.b_batched = walk.b_batches > 1;
@@ -359,13 +349,18 @@ cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const cha
   p.k_blocks = static_cast<int>((d.k + BK - 1) / BK);
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
-  p.raster_group = 8;
+  // Tile order and L2 priorities; the environment variables exist for tuning runs.
+  static const int raster_env = [] { const char* v = std::getenv("B200BLAS_HGEMM_RASTER"); return v ? std::atoi(v) : 0; }();
+  static const int hint_env = [] { const char* v = std::getenv("B200BLAS_HGEMM_L2HINT"); return v ? std::atoi(v) : -1; }();
+  p.raster_group = raster_env > 0 ? raster_env : 8;
+  p.hint_a = hint_env >= 0 ? hint_env / 10 : 0;
+  p.hint_b = hint_env >= 0 ? hint_env % 10 : 0;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   // Half-empty pair tiles waste a whole SM: leave problems whose last row of pair tiles is at most half full, and
   // that have few tiles, to the single-CTA kernel.
   const long long single_tiles = ((d.m + BM - 1) / BM) * p.tiles_n * p.batches;
-  if (single_tiles < 2 * tiles && tiles < 148) return cudaErrorNotSupported;
+  if (single_tiles < 2 * tiles && tiles < sm_count()) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
   if (!encode_operand_map(&map_a, 2, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))

@@ -23,7 +23,7 @@
 //
 // Roles (640 threads, five warpgroups with re-balanced register budgets): warp 0 TMA producer, warp 1 MMA issuer
 // and TMEM owner (warps 2-3 idle), warps 4-11 split, warps 12-19 drain + epilogue.
-// All waits are bounded; on expiry a code is left in g_tc32_status and the CTA drains and exits.
+// All waits are bounded; on expiry a code is left in the status block and the CTA drains and exits.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -33,6 +33,7 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "../runtime_state.h"
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -52,9 +53,8 @@ static_assert(128 * 40 + 256 * 56 + 256 * 160 <= NUM_THREADS * LAUNCH_REGS, "reg
 constexpr int CHUNK_KB = 4;  // K blocks accumulated inside the tensor cores before a partial is drained
 constexpr int TMEM_COLS = 512;
 
-__device__ unsigned int g_tc32_status[4];
-
 struct Tc32Params {
+  unsigned int* status;  // where an expired bounded wait is reported (mapped host memory), or null
   float* c;
   long long ldc;
   int m, n, k;
@@ -191,7 +191,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else gemm_tile(tile, tm, tn, z);
         const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_status)) { ok = false; break; }
+          if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
           if (GATHER) {
             mbar_arrive(raw_full(stage));  // nothing to load: tell the split warps the stage is theirs
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -241,12 +241,12 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, ++chunk_index) {
           const int part = chunk_index & 1;
           const uint32_t part_phase = (chunk_index >> 1) & 1u;
-          if (!mbar_wait(part_free(part), part_phase ^ 1u, abort_flag, 2u, g_tc32_status)) { ok = false; break; }
+          if (!mbar_wait(part_free(part), part_phase ^ 1u, abort_flag, 2u, p.status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(part * (TMEM_COLS / 2));
           const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
           for (int kb = kb0; kb < kb_end; ++kb) {
-            if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, g_tc32_status)) { ok = false; break; }
+            if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, p.status)) { ok = false; break; }
             tcgen05_fence_after();
             // K-major: rows of 128 B along K (16-byte-chunk swizzle), advance 8 floats = 32 B per MMA.
             // MN-major: one 128-byte row per k (32-byte-chunk swizzle, atoms of four k = 512 B), eight k = 1024 B
@@ -293,7 +293,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int kb0 = 0; kb0 < p.k_blocks; kb0 += CHUNK_KB, ++chunk_index) {
         const int part = chunk_index & 1;
         const uint32_t part_phase = (chunk_index >> 1) & 1u;
-        ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, g_tc32_status);
+        ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
@@ -386,7 +386,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if ((kbg & 1) != group) continue;
           const int st = kbg % STAGES;
           const uint32_t ph = static_cast<uint32_t>(kbg / STAGES) & 1u;
-          ok = mbar_wait(raw_full(st), ph, abort_flag, 5u, g_tc32_status);
+          ok = mbar_wait(raw_full(st), ph, abort_flag, 5u, p.status);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + st * C::STAGE_BYTES);
@@ -395,7 +395,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int c = gt; c < CHUNKS_ALL; c += 128) {
             const float4 x = main_ptr[c];
             float4 hi, lo;
-            hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
+            hi.x = to_tf32_big(x.x); hi.y = to_tf32_big(x.y); hi.z = to_tf32_big(x.z); hi.w = to_tf32_big(x.w);
             lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z);
             lo.w = to_tf32(x.w - hi.w);
             main_ptr[c] = hi;
@@ -500,7 +500,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const int row = sw + 8 * j;
               off = row * 128 + (((lane >> 2) ^ (row & 7)) << 4) + (lane & 3) * 4;
             }
-            const float hi = to_tf32(v[j]);
+            const float hi = to_tf32_big(v[j]);
             *reinterpret_cast<float*>(main_tile + off) = hi;
             *reinterpret_cast<float*>(lo_tile + off) = to_tf32(v[j] - hi);
           }
@@ -512,7 +512,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         gather_plain(gb, b_src, p.ldb, B_MN, tn * BN, p.n, 0);
       }
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_status);
+        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES);
@@ -525,10 +525,10 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int k = kr + 16 * u;
             const int f4 = ((pg >> 2) * 4096 + k * 128 + (((pg & 3) ^ (k & 3)) << 5)) >> 4;
             float4 hi0, hi1, lo0, lo1;
-            hi0.x = to_tf32(gathered[u][0]); hi0.y = to_tf32(gathered[u][1]);
-            hi0.z = to_tf32(gathered[u][2]); hi0.w = to_tf32(gathered[u][3]);
-            hi1.x = to_tf32(gathered[u][4]); hi1.y = to_tf32(gathered[u][5]);
-            hi1.z = to_tf32(gathered[u][6]); hi1.w = to_tf32(gathered[u][7]);
+            hi0.x = to_tf32_big(gathered[u][0]); hi0.y = to_tf32_big(gathered[u][1]);
+            hi0.z = to_tf32_big(gathered[u][2]); hi0.w = to_tf32_big(gathered[u][3]);
+            hi1.x = to_tf32_big(gathered[u][4]); hi1.y = to_tf32_big(gathered[u][5]);
+            hi1.z = to_tf32_big(gathered[u][6]); hi1.w = to_tf32_big(gathered[u][7]);
             lo0.x = to_tf32(gathered[u][0] - hi0.x); lo0.y = to_tf32(gathered[u][1] - hi0.y);
             lo0.z = to_tf32(gathered[u][2] - hi0.z); lo0.w = to_tf32(gathered[u][3] - hi0.w);
             lo1.x = to_tf32(gathered[u][4] - hi1.x); lo1.y = to_tf32(gathered[u][5] - hi1.y);
@@ -551,7 +551,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int c = CHUNK_FIRST + t; c < CHUNKS; c += 256) {
           const float4 x = main_ptr[c];
           float4 hi, lo;
-          hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
+          hi.x = to_tf32_big(x.x); hi.y = to_tf32_big(x.y); hi.z = to_tf32_big(x.z); hi.w = to_tf32_big(x.w);
           lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z); lo.w = to_tf32(x.w - hi.w);
           main_ptr[c] = hi;
           lo_ptr[c] = lo;
@@ -590,15 +590,6 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
 
 }  // namespace
 
-cudaError_t tc_f32_status(unsigned int out[4], bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc32_status, sizeof(unsigned int) * 4);
-  if (e == cudaSuccess && clear && out[0] != 0) {
-    const unsigned int zero[4] = {0, 0, 0, 0};
-    e = cudaMemcpyToSymbol(g_tc32_status, zero, sizeof(zero));
-  }
-  return e;
-}
-
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
@@ -623,17 +614,14 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
 
   // Tile width: 256 columns amortise the operand traffic best; 128 columns give twice as many tiles and one more
   // pipeline stage, which wins while 256-wide tiles would leave SMs idle.
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  const int device_sms = sm_count();
+  if (device_sms <= 0) return cudaErrorNotSupported;
   const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256) * walk.batches;
-  int bn = (!gathered && tiles_wide >= 2LL * sm_counts[dev]) ? 256 : 128;
+  int bn = (!gathered && tiles_wide >= 2LL * device_sms) ? 256 : 128;
   // Small problems: when twice as many tiles still fit the machine in one wave, 64-column tiles put twice as many
   // SMs to work (1024^3: 64 -> 128 CTAs, 56 -> 66 TFLOP/s).
   const long long tiles_128 = ((d.m + BM - 1) / BM) * ((d.n + 127) / 128) * walk.batches;
-  if (!gathered && bn == 128 && 2 * tiles_128 <= sm_counts[dev]) bn = 64;
+  if (!gathered && bn == 128 && 2 * tiles_128 <= device_sms) bn = 64;
 
   CUtensorMap map_a, map_b;
   if (gathered) {
@@ -647,6 +635,7 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   }
 
   Tc32Params p = {};
+  p.status = tc_status_device();
   p.a = a; p.b = b;
   p.lda = d.lda; p.ldb = d.ldb;
   p.batches = walk.batches;
@@ -667,7 +656,7 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   if (tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
-  int sms = sm_counts[dev];
+  int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
 
@@ -724,7 +713,7 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
   constexpr int BN = 64;
   if (d.m > BN || d.m < 16 || d.n < 64 || d.k < 32 || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const long long tiles = ((d.n + BM - 1) / BM) * walk.batches;
-  if (tiles < 148 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  if (tiles < sm_count() || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
   if (static_cast<double>(d.m) * d.n * d.k * walk.batches < 134217728.0) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
@@ -740,6 +729,7 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
     return cudaErrorNotSupported;
 
   Tc32Params p = {};
+  p.status = tc_status_device();
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.n); p.n = static_cast<int>(d.m); p.k = static_cast<int>(d.k);
@@ -758,12 +748,9 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
   p.c_rowmajor = 1;
   p.c_vec4 = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0 && d.ldc % 4 == 0 && walk.c_stride % 4 == 0) ? 1 : 0;
 
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  int sms = sm_counts[dev];
+  const int device_sms = sm_count();
+  if (device_sms <= 0) return cudaErrorNotSupported;
+  int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   *name = "tc_f32_3xtf32_narrow_128x64x32";
@@ -795,6 +782,7 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   if (!encode_operand_map(&map_b, 4, weights, d.n, d.k, d.ldb, false, BN, 1, 0)) return cudaErrorNotSupported;
 
   Tc32Params p = {};
+  p.status = tc_status_device();
   p.c = static_cast<float*>(d.c) + d.c_off;
   p.ldc = d.ldc;
   p.m = static_cast<int>(d.m); p.n = static_cast<int>(d.n); p.k = static_cast<int>(d.k);
@@ -810,12 +798,9 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   p.batch = static_cast<int>(d.batch);
   p.conv = d.conv;
 
-  static int sm_counts[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (sm_counts[dev] == 0) cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  int sms = sm_counts[dev];
+  const int device_sms = sm_count();
+  if (device_sms <= 0) return cudaErrorNotSupported;
+  int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   *name = "tc_conv_f32_3xtf32_128x128x32";

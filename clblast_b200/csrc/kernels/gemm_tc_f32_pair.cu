@@ -24,6 +24,7 @@
 
 #include "../tc_host.h"
 #include "launchers.h"
+#include "../runtime_state.h"
 #include "tc_common.cuh"
 
 namespace b200 {
@@ -50,9 +51,8 @@ constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // main (raw -> hi in plac
 constexpr int STAGES = 3;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
-__device__ unsigned int g_tc32_pair_status[4];
-
 struct PairParams {
+  unsigned int* status;  // where an expired bounded wait is reported (mapped host memory), or null
   float* c;
   long long ldc;
   int m, n, k;
@@ -148,7 +148,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const int b_row0 = tn * BN + static_cast<int>(rank) * BN_HALF;
           const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
           for (int kb = 0; kb < p.k_blocks; ++kb) {
-            if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, g_tc32_pair_status)) { ok = false; break; }
+            if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
             mbar_arrive_expect_tx(raw_full(stage), A_BYTES + B_BYTES);
             if (A_MN) {
 #pragma unroll
@@ -191,7 +191,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, ++chunk_index) {
             const int part = chunk_index & 1;
             const uint32_t part_phase = (chunk_index >> 1) & 1u;
-            if (!mbar_wait_cluster(part_free(part), part_phase ^ 1u, abort_flag, 2u, g_tc32_pair_status)) {
+            if (!mbar_wait_cluster(part_free(part), part_phase ^ 1u, abort_flag, 2u, p.status)) {
               ok = false;
               break;
             }
@@ -199,7 +199,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(part * (TMEM_COLS / 2));
             const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
             for (int kb = kb0; kb < kb_end; ++kb) {
-              if (!mbar_wait_cluster(split_full(stage), phase, abort_flag, 3u, g_tc32_pair_status)) {
+              if (!mbar_wait_cluster(split_full(stage), phase, abort_flag, 3u, p.status)) {
                 ok = false;
                 break;
               }
@@ -248,7 +248,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int kb0 = 0; kb0 < p.k_blocks; kb0 += CHUNK_KB, ++chunk_index) {
         const int part = chunk_index & 1;
         const uint32_t part_phase = (chunk_index >> 1) & 1u;
-        ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, g_tc32_pair_status);
+        ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
@@ -306,7 +306,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if ((kbg & 1) != group) continue;
         const int stage = kbg % STAGES;
         const uint32_t phase = static_cast<uint32_t>(kbg / STAGES) & 1u;
-        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, g_tc32_pair_status);
+        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * STAGE_BYTES);
@@ -315,7 +315,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int c = gt; c < CHUNKS; c += 128) {
           const float4 x = main_ptr[c];
           float4 hi, lo;
-          hi.x = to_tf32(x.x); hi.y = to_tf32(x.y); hi.z = to_tf32(x.z); hi.w = to_tf32(x.w);
+          hi.x = to_tf32_big(x.x); hi.y = to_tf32_big(x.y); hi.z = to_tf32_big(x.z); hi.w = to_tf32_big(x.w);
           lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z); lo.w = to_tf32(x.w - hi.w);
           main_ptr[c] = hi;
           lo_ptr[c] = lo;
@@ -341,7 +341,7 @@ int resident_pairs() {
   auto kernel = sgemm_3xtf32_pair_kernel<A_MN, B_MN>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.gridDim = dim3(2 * sm_count(), 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = SMEM_BYTES;
   cudaLaunchAttribute attr[1];
@@ -368,12 +368,8 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
   cudaFuncAttributes fattr;
   if (cudaFuncGetAttributes(&fattr, kernel) != cudaSuccess) return cudaErrorNotSupported;
   if (fattr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
-  static int pairs_of_device[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorNotSupported;
-  if (pairs_of_device[dev] == 0) pairs_of_device[dev] = resident_pairs<A_MN, B_MN>();
-  int pairs = pairs_of_device[dev];
+  static std::atomic<int> pairs_of_device[kMaxDevices];
+  int pairs = per_device(pairs_of_device, &resident_pairs<A_MN, B_MN>);
   if (pairs <= 0) return cudaErrorNotSupported;
   if (sm_budget() > 0 && sm_budget() / 2 < pairs) pairs = sm_budget() / 2;
   if (pairs <= 0) return cudaErrorNotSupported;
@@ -385,15 +381,6 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
 }
 
 }  // namespace
-
-cudaError_t tc_f32_pair_status(unsigned int out[4], bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_tc32_pair_status, sizeof(unsigned int) * 4);
-  if (e == cudaSuccess && clear && out[0] != 0) {
-    const unsigned int zero[4] = {0, 0, 0, 0};
-    e = cudaMemcpyToSymbol(g_tc32_pair_status, zero, sizeof(zero));
-  }
-  return e;
-}
 
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
@@ -414,6 +401,7 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   if ((walk.a_stride % 4) || (walk.b_stride % 4)) return cudaErrorNotSupported;
 
   PairParams p;
+  p.status = tc_status_device();
   p.batches = walk.batches;
   p.a_batched = walk.a_batches > 1;
   p.b_batched = walk.b_batches > 1;
@@ -432,7 +420,7 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   // Enough 256 x 256 tiles to give every pair of SMs two: below that the 128-wide single-CTA tiles fill the
   // machine better.
-  if (tiles < 148 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  if (tiles < sm_count() || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
   if (!encode_operand_map(&map_a, 4, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))

@@ -4,6 +4,7 @@
 #include <cuda_runtime_api.h>
 
 #include "gemm_desc.h"
+#include "../runtime_state.h"
 
 namespace b200 {
 
@@ -20,17 +21,16 @@ cudaError_t launch_simt_c64(const GemmDesc& d, cudaStream_t stream, const char**
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name);
 // The same on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles shared by two SMs), tried first.
 cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const char** name);
-cudaError_t tc_f16_pair_status(unsigned int out[4], bool clear);
 
 // DGEMM on the FP64 tensor-core instructions (mma.sync m8n8k4). Same contract as launch_tc_f16.
 cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char** name);
 
 // Tensor-core SGEMM (error-compensated 3xTF32). Same contract as launch_tc_f16.
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
-cudaError_t tc_f32_status(unsigned int out[4], bool clear);
+
 // The same on CTA pairs (256 x 256 tiles shared by two SMs), tried first for large problems.
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name);
-cudaError_t tc_f32_pair_status(unsigned int out[4], bool clear);
+
 // Batches of narrow problems (at most 64 rows) on the same kernel, computed as the transposed problem.
 cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const char** name);
 // Tensor-core Convgemm (same kernel, op(A) gathered from the image by the split warps).
@@ -39,10 +39,6 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
 // Streaming kernel for large batches of small fp32 problems (cp.async double buffering across the batch). Returns
 // cudaErrorNotSupported without launching when the call does not meet its shape and alignment requirements.
 cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
-
-// Reads (and optionally clears) the tensor-core kernel's device status words: out[0] != 0 means a bounded wait
-// expired in some CTA (1 producer, 2 accumulator-free, 3 operands-ready, 4 accumulator-ready), out[1] is the block.
-cudaError_t tc_f16_status(unsigned int out[4], bool clear);
 
 // Number of SMs persistent kernels may occupy (0 = all); set through b200blas_set_sm_budget.
 int sm_budget();
@@ -69,12 +65,13 @@ inline int pick_simt(const GemmDesc& d, const SimtConfig* cfgs, int count) {
     ctas[i] = tiles / cfgs[i].groups;
     if (ctas[i] > most_ctas) most_ctas = ctas[i];
   }
-  // A problem too small to fill the 148 SMs with any configuration is latency-bound: only padding matters then.
-  const bool tiny = most_ctas < 148.0;
+  // A problem too small to fill the SMs with any configuration is latency-bound: only padding matters then.
+  const double sms = sm_count() > 0 ? sm_count() : 148.0;
+  const bool tiny = most_ctas < sms;
   int best = 0;
   double best_score = -1.0;
   for (int i = 0; i < count; ++i) {
-    const double fill = (tiny || ctas[i] >= 148.0) ? 1.0 : ctas[i] / 148.0;
+    const double fill = (tiny || ctas[i] >= sms) ? 1.0 : ctas[i] / sms;
     const double score = quality[i] * fill;
     if (score > best_score) {
       best_score = score;

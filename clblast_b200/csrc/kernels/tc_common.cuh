@@ -36,6 +36,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Leaves the code of an expired wait in the status block (mapped host memory, so plain stores rather than atomics;
+// when several CTAs give up, any one of their reports is as good as another). `status` may be null.
+__device__ __forceinline__ void report_expired_wait(unsigned int* status, unsigned code, uint32_t bar) {
+  if (status == nullptr) return;
+  volatile unsigned int* s = status;
+  if (s[0] == 0u) {
+    s[1] = blockIdx.x;
+    s[2] = bar;
+    s[0] = code;
+  }
+}
+
 // Bounded wait. Returns false when the wait expired (the code is recorded in status[0..2], first writer wins) or
 // another role of the CTA already raised the abort flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned code,
@@ -48,10 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       if (clock64() - start > kWaitCycles) {
         *abort_flag = 1;
-        if (atomicCAS(&status[0], 0u, code) == 0u) {
-          status[1] = blockIdx.x;
-          status[2] = bar;
-        }
+        report_expired_wait(status, code, bar);
         return false;
       }
     }
@@ -159,7 +168,15 @@ __device__ __forceinline__ float to_tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
 }
-
+// The "big" part of the 3xTF32 split: as above, but a finite value in the last 2^-11 of the fp32 range, which
+// round-to-nearest would turn into infinity, becomes the largest finite TF32 value (the remainder goes into the
+// "small" part like any other rounding error). An infinite input also becomes that value; its small part is then
+// infinite, so the infinity still reaches every output it touches.
+__device__ __forceinline__ float to_tf32_big(float x) {
+  uint32_t r;
+  asm("cvt.rna.satfinite.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
 
 // ---- results leaving through shared memory and TMA stores ---------------------------------------------------------
 
@@ -184,10 +201,7 @@ __device__ __forceinline__ bool wait_old_block(uint32_t bar, uint32_t parity, un
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (clock64() - start > kWaitCycles) {
-      if (atomicCAS(&status[0], 0u, 6u) == 0u) {
-        status[1] = blockIdx.x;
-        status[2] = bar;
-      }
+      report_expired_wait(status, 6u, bar);
       return false;
     }
   }
@@ -226,6 +240,31 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// L2 eviction priority for the lines a TMA load brings in: 0 normal, 1 evict-first (streamed data), 2 evict-last
+// (data other CTAs will ask for again soon).
+__device__ __forceinline__ uint64_t l2_policy(int kind) {
+  uint64_t p;
+  if (kind == 1) {
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  } else if (kind == 2) {
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  } else {
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  }
+  return p;
+}
+
+// The same load with an L2 eviction policy attached.
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                      int y, int z, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5}], [%2], %6;"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
 // Arrives, once the MMAs issued so far have completed, on the barrier at this offset in both CTAs of the pair.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
@@ -257,10 +296,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
       if (*abort_flag) return false;
       if (clock64() - start > kWaitCycles) {
         *abort_flag = 1;
-        if (atomicCAS(&status[0], 0u, code) == 0u) {
-          status[1] = blockIdx.x;
-          status[2] = bar;
-        }
+        report_expired_wait(status, code, bar);
         return false;
       }
     }

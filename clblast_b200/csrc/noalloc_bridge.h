@@ -23,5 +23,8 @@ int prepare_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, s
                     unsigned char* host_block, size_t host_capacity, GemmDesc* out, BatchedTables* tables);
 void patch_batched_tables(GemmDesc* d, const BatchedTables& t, const unsigned char* device_block);
 cudaError_t dispatch_desc(const GemmDesc& d, cudaStream_t stream);
+// After the stream of a launch has been synchronised: kUnexpectedError when a tensor-core kernel reported an expired
+// wait, else 0.
+int status_after_sync();
 
 }  // namespace b200

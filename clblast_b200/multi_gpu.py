@@ -88,3 +88,147 @@ def gemm_strided_batched_sharded(gemm_strided_batched: Callable, world: int, ran
                                   a_offset + b0 * a_stride, a_ld, a_stride, b_buffer, b_offset + b0 * b_stride, b_ld,
                                   b_stride, beta, c_buffer, c_offset + b0 * c_stride, c_ld, c_stride, nb, **kwargs)
     return status, b0, nb
+
+
+# ---- replication of the unsplit operand with the copy engines ---------------------------------------------------
+
+def binomial_tree(world: int, rank: int, root: int = 0):
+    """(parent, children) of ``rank`` in the binomial broadcast tree rooted at ``root``.
+
+    Children are listed farthest first, the order in which a node forwards: with 8 ranks the root sends to 4, 2, 1;
+    rank 4 to 6, 5; ranks 2 and 6 to 3 and 7. Every rank receives once; no rank is more than ceil(log2(world)) hops from the root."""
+    if world < 1 or not 0 <= rank < world or not 0 <= root < world:
+        raise ValueError("invalid world / rank / root")
+    rel = (rank - root) % world
+    parent = None
+    mask = 1
+    while mask < world:
+        if rel & mask:
+            parent = ((rel - mask) + root) % world
+            break
+        mask <<= 1
+    children = []
+    m = mask >> 1
+    while m >= 1:
+        if rel + m < world:
+            children.append(((rel + m) + root) % world)
+        m >>= 1
+    return parent, children
+
+
+class CopyEngineFanout:
+    """Replicates a buffer from ``root`` to every rank of one node, step after step, without a collective kernel.
+
+    Each rank owns a ring of ``len(buffers)`` equally sized device buffers. In step s (1, 2, ...) the contents of the
+    root's ``buffers[s % depth]`` travel down a binomial tree: a node waits until its parent's copy has landed
+    (a 32-bit flag in its own memory, waited for by the stream front-end), forwards the buffer to its children with
+    ``cudaMemcpyAsync`` into their mapped memory (copy engines, NVLink), and raises their flags. A child tells its
+    parent when it is done with a ring slot, so with two buffers the transfer of step s overlaps the compute of
+    step s - 1 on every rank while the compute kernels keep all SMs and read local memory only.
+
+    ``step_begin`` enqueues the step's forwarding on an internal copy stream and makes the compute stream wait for the
+    step's data; ``step_end`` is called after the compute that reads the buffer has been enqueued."""
+
+    MAX_STEPS = 1 << 16
+
+    def __init__(self, dist, buffers, root: int = 0):
+        import ctypes
+
+        import torch
+
+        from ._lib import lib
+
+        self._ct, self._torch, self._L = ctypes, torch, lib()
+        self.world, self.rank, self.root = dist.get_world_size(), dist.get_rank(), root
+        self.depth = len(buffers)
+        if self.depth < 1 or any(b.numel() * b.element_size() != buffers[0].numel() * buffers[0].element_size()
+                                 for b in buffers):
+            raise ValueError("the ring needs at least one buffer, all of one size")
+        self.buffers = list(buffers)
+        self.nbytes = buffers[0].numel() * buffers[0].element_size()
+        self.parent, self.children = binomial_tree(self.world, self.rank, root)
+        dev = buffers[0].device
+        # word 0: newest step whose data has landed here; word 1 + i: newest step child i has finished with
+        self.flags = torch.zeros(64, dtype=torch.int32, device=dev)
+        self.seq = torch.arange(self.MAX_STEPS, dtype=torch.int32, device=dev)   # source words of the flag copies
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.step = 0
+        self._fwd_done = None
+        torch.cuda.synchronize(dev)
+
+        mine = {"buffers": [self._export(b) for b in self.buffers], "flags": self._export(self.flags)}
+        table = [None] * self.world
+        dist.all_gather_object(table, mine)
+        self._opened = {}
+        self.child_buffers = [[self._open(table[c]["buffers"][i]) for i in range(self.depth)] for c in self.children]
+        self.child_flags = [self._open(table[c]["flags"]) for c in self.children]
+        self.parent_flags = self._open(table[self.parent]["flags"]) if self.parent is not None else None
+        if self.parent is not None:
+            _, siblings = binomial_tree(self.world, self.parent, root)
+            self.slot_at_parent = 1 + siblings.index(self.rank)
+        dist.barrier()
+
+    def _export(self, tensor):
+        handle = (self._ct.c_ubyte * 64)()
+        offset = self._ct.c_size_t(0)
+        st = self._L.b200blas_ipc_export(tensor.data_ptr(), handle, self._ct.byref(offset))
+        if st != 0:
+            raise RuntimeError(f"exporting a device allocation failed with status {st}")
+        return bytes(handle), offset.value
+
+    def _open(self, exported):
+        handle, offset = exported
+        if handle not in self._opened:   # one mapping per peer allocation, however many buffers live in it
+            out = self._ct.c_void_p()
+            raw = (self._ct.c_ubyte * 64).from_buffer_copy(handle)
+            st = self._L.b200blas_ipc_open(raw, 0, self._ct.byref(out))
+            if st != 0:
+                raise RuntimeError(f"mapping a peer allocation failed with status {st}")
+            self._opened[handle] = out.value
+        return self._opened[handle] + offset
+
+    def _check(self, st, what):
+        if st != 0:
+            raise RuntimeError(f"{what} failed with status {st}")
+
+    def step_begin(self, compute_stream, ready_event=None):
+        """Starts step ``self.step + 1``. On the root, ``ready_event`` (optional) marks the point where the step's
+        buffer has been produced. Returns the local buffer that holds the step's data once ``compute_stream`` runs."""
+        torch, L = self._torch, self._L
+        self.step += 1
+        s = self.step
+        if s >= self.MAX_STEPS:
+            raise RuntimeError("step counter exhausted")
+        slot = s % self.depth
+        cs = self.copy_stream.cuda_stream
+        if self.parent is not None:
+            self._check(L.b200blas_stream_wait_flag(cs, self.flags.data_ptr(), s), "stream wait")
+            self._check(L.b200blas_stream_wait_flag(compute_stream.cuda_stream, self.flags.data_ptr(), s), "stream wait")
+        elif ready_event is not None:
+            self.copy_stream.wait_event(ready_event)
+        for i, child in enumerate(self.children):
+            if s > self.depth:   # the child must have finished with the slot's previous contents
+                self._check(L.b200blas_stream_wait_flag(cs, self.flags.data_ptr() + 4 * (1 + i), s - self.depth),
+                            "stream wait")
+            self._check(L.b200blas_stream_copy(cs, self.child_buffers[i][slot], self.buffers[slot].data_ptr(),
+                                               self.nbytes), "peer copy")
+            self._check(L.b200blas_stream_copy(cs, self.child_flags[i], self.seq.data_ptr() + 4 * s, 4), "flag copy")
+        if self.children:
+            self._fwd_done = torch.cuda.Event()
+            self._fwd_done.record(self.copy_stream)
+        return self.buffers[slot]
+
+    def step_end(self, compute_stream):
+        """Releases the step's ring slot to the parent once the compute enqueued so far and this rank's own forwards
+        of the step have finished."""
+        if self.children and self._fwd_done is not None:
+            compute_stream.wait_event(self._fwd_done)
+        if self.parent is not None:
+            self._check(self._L.b200blas_stream_copy(compute_stream.cuda_stream, self.parent_flags + 4 * self.slot_at_parent,
+                                                     self.seq.data_ptr() + 4 * self.step, 4), "flag copy")
+
+    def close(self):
+        self._torch.cuda.synchronize()
+        for base in self._opened.values():
+            self._L.b200blas_ipc_close(base, 0)
+        self._opened = {}

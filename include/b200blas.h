@@ -57,7 +57,11 @@ int b200blas_gemm_batched(int dtype, int layout, int a_transpose, int b_transpos
  *   - all calls on one GPU share the array (about 224 KB per GPU, held until the process exits) and it keeps the
  *     last call's tables, so calls that could overlap on the GPU (other streams, other threads) must be ordered
  *     by the caller;
- *   - the first call on each device resolves the array's device address; make it before any stream capture. */
+ *   - the first call under each CUDA context resolves the array's device address in that context;
+ *   - a stream that is being captured is refused with kUnexpectedError (-2039) before anything is enqueued: the
+ *     host block that the table copy reads is reused by the next call;
+ *   - with `wait != 0` an expired bounded wait of a tensor-core kernel is reported as kUnexpectedError, as the
+ *     regular entry point does; with `wait == 0` use b200blas_tensor_core_status after synchronising. */
 #define B200BLAS_STATIC_MAX_BATCHES 4096
 int b200blas_gemm_batched_static(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n,
                                  size_t k, const void* alphas, const void* a, const size_t* a_offsets, size_t a_ld,
@@ -95,6 +99,34 @@ int b200blas_retrieve_parameters(int device, const char* kernel_name, int precis
  * GEMM with a collective or a copy kernel on another stream leaves those a few SMs this way. Process-wide.
  * No counterpart in the reference. */
 void b200blas_set_sm_budget(int sms);
+
+/* Multi-GPU building blocks (no counterpart in the reference, which is a single-device library). The sharded GEMM
+ * needs the operand that is not split on every GPU; these calls move it with the copy engines, so that no collective
+ * kernel competes with the persistent GEMM kernels for SMs. Kernels of this library only ever read local memory.
+ *   b200blas_ipc_export: 64-byte handle of the device allocation that contains `device_ptr`, plus the pointer's
+ *     byte offset inside it; another process of the same node maps it with b200blas_ipc_open (peer access is
+ *     enabled on demand) and unmaps it with b200blas_ipc_close(pointer, offset).
+ *   b200blas_stream_copy: cudaMemcpyAsync with the direction inferred from the pointers; `dst` may be a mapped
+ *     peer pointer. One call per copy.
+ *   b200blas_stream_wait_flag: work enqueued on `stream` after this call starts once the 32-bit word at `flag`
+ *     (LOCAL device memory, 4-byte aligned) is >= `value`; no SM is occupied while waiting. The writer is a peer's
+ *     4-byte b200blas_stream_copy into that word, ordered after the payload copy on the peer's stream.
+ *   b200blas_stream_write_flag: stream-ordered store of `value` to a 32-bit word in local device memory.
+ * All return 0 or a CUDA error number. */
+int b200blas_ipc_export(const void* device_ptr, unsigned char handle[64], size_t* offset);
+int b200blas_ipc_open(const unsigned char handle[64], size_t offset, void** device_ptr);
+int b200blas_ipc_close(void* device_ptr, size_t offset);
+int b200blas_stream_copy(void* stream, void* dst, const void* src, size_t bytes);
+int b200blas_stream_wait_flag(void* stream, const void* flag, uint32_t value);
+int b200blas_stream_write_flag(void* stream, void* flag, uint32_t value);
+
+/* The tensor-core kernels bound every wait on a barrier; a wait that expires (a lost copy, a defect) makes the
+ * kernel leave a code in a status block and return instead of hanging. Synchronous calls check the block themselves
+ * and return kUnexpectedError. Callers that enqueue on their own stream (`async != 0`) call this after that stream
+ * has been synchronised: it copies the block (code, block index, barrier address, 0) to `out` (may be NULL), clears
+ * it when `clear != 0`, and returns 0 when no wait has expired since the last clear, kUnexpectedError otherwise.
+ * No counterpart in the reference. */
+int b200blas_tensor_core_status(unsigned int out[4], int clear);
 
 /* Introspection for tests and benchmarks (no counterpart in the reference). */
 

@@ -92,3 +92,29 @@ def test_column_sharded_gemm_over_gloo(tmp_path):
     assert covered == n
     batches = [tuple(np.load(tmp_path / f"batch_{r}.npy")) for r in range(world)]
     assert batches == [(0, 4), (4, 3)]
+
+
+def test_binomial_tree_reaches_every_rank_once():
+    from clblast_b200.multi_gpu import binomial_tree
+    for world in (1, 2, 3, 4, 5, 8, 13):
+        for root in (0, world - 1):
+            parents = {}
+            for r in range(world):
+                parent, children = binomial_tree(world, r, root)
+                parents[r] = parent
+                for c in children:
+                    assert binomial_tree(world, c, root)[0] == r     # both sides agree on every edge
+            assert parents[root] is None
+            assert sum(p is None for p in parents.values()) == 1
+            depth = 0
+            for r in range(world):                                   # every rank reaches the root
+                hops, x = 0, r
+                while parents[x] is not None:
+                    x = parents[x]
+                    hops += 1
+                    assert hops <= world
+                assert x == root
+                depth = max(depth, hops)
+            assert depth <= (world - 1).bit_length()
+    assert binomial_tree(8, 0) == (None, [4, 2, 1])
+    assert binomial_tree(8, 4) == (0, [6, 5])

@@ -159,3 +159,49 @@ def test_config2_large_squares_sampled(cuda, n):
         assert (np.abs(got - want) / (1.5 * mag + 0.5)).max() < 2.0 ** -20
         # the padding between columns is untouched
         assert torch.equal(c.view(n, ld)[:, n:], c0.view(n, ld)[:, n:])
+
+
+@pytest.mark.parametrize("shift", (100, 120))
+def test_wide_dynamic_range_operands(cuda, shift):
+    """A scaled by 2^-shift, B by 2^+shift: every product is well scaled, so the fp32 FFMA chain of the reference gives
+    fp32-level results. The split keeps that level as long as the small part x - tf32(x) (at most 2^-11 |x|) of the
+    contributing entries is a normal fp32 number, i.e. for |x| >= 2^-115: asserted at 2^-100. Below that the small
+    parts become subnormal and the guaranteed level is the TF32 one (2^-10 of sum |a||b|): pinned at 2^-120."""
+    torch = cuda
+    n = 512
+    rng = np.random.default_rng(shift)
+    a = (rng.uniform(-1, 1, n * n) * 2.0 ** -shift).astype(np.float32)
+    b = (rng.uniform(-1, 1, n * n) * 2.0 ** shift).astype(np.float32)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    c = torch.full((n * n,), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    assert cb.Gemm(H.COL, H.NO, H.NO, n, n, n, 1.0, da, 0, n, db, 0, n, 0.0, c, 0, n) == 0
+    assert cb.last_kernel().startswith("tc_f32")
+    want = b.astype(np.float64).reshape(n, n) @ a.astype(np.float64).reshape(n, n)   # [j][i] = C(i, j)
+    mag = np.abs(b.astype(np.float64)).reshape(n, n) @ np.abs(a.astype(np.float64)).reshape(n, n)
+    got = c.cpu().numpy().astype(np.float64).reshape(n, n)
+    assert np.isfinite(got).all()
+    err = (np.abs(got - want) / mag).max()
+    assert err < (2.0 ** -20 if shift == 100 else 2.0 ** -9), err
+
+
+def test_values_next_to_the_largest_finite_float(cuda):
+    """Entries within the last 2^-11 of the fp32 range would round to infinity as TF32; the split saturates them
+    instead, so a product that is finite in fp32 arithmetic stays finite and accurate."""
+    torch = cuda
+    n = 512
+    rng = np.random.default_rng(3)
+    a = rng.uniform(-1, 1, n * n).astype(np.float32)
+    big = np.float32(3.4028234e38)
+    a[::97] = big * np.where(rng.uniform(size=a[::97].size) < 0.5, -1, 1).astype(np.float32)
+    b = (rng.uniform(-1, 1, n * n) * 2.0 ** -12).astype(np.float32)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    c = torch.full((n * n,), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    assert cb.Gemm(H.COL, H.NO, H.NO, n, n, n, 1.0, da, 0, n, db, 0, n, 0.0, c, 0, n) == 0
+    assert cb.last_kernel().startswith("tc_f32")
+    want = b.astype(np.float64).reshape(n, n) @ a.astype(np.float64).reshape(n, n)
+    mag = np.abs(b.astype(np.float64)).reshape(n, n) @ np.abs(a.astype(np.float64)).reshape(n, n)
+    got = c.cpu().numpy().astype(np.float64).reshape(n, n)
+    assert np.isfinite(got).all()
+    assert (np.abs(got - want) / mag).max() < 2.0 ** -20

@@ -59,3 +59,53 @@ def test_static_table_variant_rejects_oversized_batches(cuda):
     st = cb.GemmBatchedStatic(H.COL, H.NO, H.NO, 2, 2, 2, [1.0] * batch, buf, [0] * batch, 2, buf, [0] * batch, 2,
                               [0.0] * batch, buf, [0] * batch, 2, batch, stream=torch.cuda.current_stream())
     assert st == cb.StatusCode.kInvalidBatchCount
+
+
+def test_static_table_variant_on_evenly_spaced_offsets_reaches_the_tensor_cores(cuda):
+    """Evenly spaced offset tables are recognised on the host and run on the tensor-core kernels; the result is
+    compared with the regular entry point (bit for bit) and directly with the fp64 oracle, two calls in a row."""
+    from oracle import cpu_oracle as oracle
+    torch = cuda
+    rng = np.random.default_rng(77)
+    stream = torch.cuda.Stream()
+    for m, n, k, batch in ((256, 256, 128, 12), (512, 256, 192, 6)):
+        a_offs = [i * m * k for i in range(batch)]
+        b_offs = [i * k * n for i in range(batch)]
+        c_offs = [i * m * n for i in range(batch)]
+        a = H.rand_buffer(rng, 32, batch * m * k, -1, 1)
+        b = H.rand_buffer(rng, 32, batch * k * n, -1, 1)
+        c = H.rand_buffer(rng, 32, batch * m * n, -1, 1)
+        alphas = [1.0 + 0.25 * i for i in range(batch)]
+        betas = [0.5 if i % 2 else 0.0 for i in range(batch)]
+        da, db = H.to_device(torch, 32, a), H.to_device(torch, 32, b)
+        dc_ref, dc_new = H.to_device(torch, 32, c), H.to_device(torch, 32, c)
+        torch.cuda.synchronize()
+        args = (H.COL, H.NO, H.NO, m, n, k, alphas, da, a_offs, m, db, b_offs, k, betas)
+        assert cb.GemmBatched(*args, dc_ref, c_offs, m, batch, precision=32) == 0
+        assert cb.GemmBatchedStatic(*args, dc_new, c_offs, m, batch, precision=32, stream=stream, wait=True) == 0
+        assert cb.last_kernel().startswith("tc_"), cb.last_kernel()
+        ref, new = H.to_host(32, dc_ref), H.to_host(32, dc_new)
+        assert np.array_equal(ref.view(np.uint8), new.view(np.uint8))
+        for i in (0, batch - 1):
+            want = oracle.gemm_f64(32, H.COL, H.NO, H.NO, m, n, k, alphas[i], a, a_offs[i], m, b, b_offs[i], k, betas[i],
+                                   c, c_offs[i], m)
+            sl = slice(c_offs[i], c_offs[i] + m * n)
+            bad, worst = oracle.count_mismatches(32, new[sl], want[sl])
+            assert bad == 0, (i, worst)
+            assert worst / (alphas[i] * k + 1.0) < 2.0 ** -20
+
+
+def test_static_table_variant_refuses_a_capturing_stream(cuda):
+    torch = cuda
+    buf = torch.zeros(64, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    before = cb.launch_count()
+    with torch.cuda.graph(graph, stream=side):
+        st = cb.GemmBatchedStatic(H.COL, H.NO, H.NO, 2, 2, 2, [1.0], buf, [0], 2, buf, [8], 2, [0.0], buf, [16], 2, 1,
+                                  stream=side, wait=False)
+    assert st == cb.StatusCode.kUnexpectedError
+    assert cb.launch_count() == before  # nothing was enqueued
+    torch.cuda.synchronize()
+    assert float(buf.abs().sum()) == 0.0
