@@ -5,11 +5,11 @@ API symbols); this package is the Python binding used by the tests and the bench
 """
 from .api import (ClearCache, Convgemm, FillCache, Gemm, GemmBatched, GemmBatchedStatic, GemmStridedBatched, GemmTempBufferSize,
                   KernelMode, Layout, OverrideParameters, Precision, RetrieveParameters, StatusCode, Transpose,
-                  last_kernel, launch_count, set_sm_budget)
+                  last_kernel, launch_count, set_sm_budget, tensor_core_status)
 from ._lib import LIB_PATH, LibraryMissing, lib
 
 __all__ = [
     "ClearCache", "Convgemm", "FillCache", "Gemm", "GemmBatched", "GemmBatchedStatic", "GemmStridedBatched", "GemmTempBufferSize",
     "KernelMode", "Layout", "OverrideParameters", "Precision", "RetrieveParameters", "StatusCode", "Transpose",
-    "last_kernel", "launch_count", "set_sm_budget", "LIB_PATH", "LibraryMissing", "lib",
+    "last_kernel", "launch_count", "set_sm_budget", "tensor_core_status", "LIB_PATH", "LibraryMissing", "lib",
 ]

@@ -6,8 +6,8 @@ once more with the arguments rank 7 of 8 passes when C is split by column blocks
 offset += j0 * ld, which puts the offsets themselves beyond 2^31 and, for SGEMM, next to 2^32).
 
 Checked: C was poisoned with NaN and beta is 0, so no NaN may remain; a grid of sampled entries (rows and columns
-forced into the first and last rows, the last column block and the last column, i.e. element indices above 2^31 and,
-for SGEMM, above 2^32 - ld) is compared with exact fp64 dot products of length K under the reference's own margins
+forced into the first and last rows, the last column block and the last column, i.e. byte offsets above 2^32 and,
+for SGEMM, element indices above 2^32 - ld) is compared with exact fp64 dot products of length K under the reference's own margins
 (test/correctness/tester.cpp:29-69) and the tight normalised bounds used for the small cases."""
 import numpy as np
 import pytest
@@ -32,12 +32,15 @@ def _fill(torch, count, dt, gen):
 
 
 def _sample_grid(rng, n, forced_rows, forced_cols, count=64):
-    rows = np.unique(np.concatenate([np.asarray(forced_rows), rng.integers(0, n, count)]))[:count]
-    cols = np.unique(np.concatenate([np.asarray(forced_cols), rng.integers(0, n, count)]))[:count]
-    return rows.astype(np.int64), cols.astype(np.int64)
+    """Sorted row and column indices: the forced ones plus random ones up to `count` each."""
+    def pick(forced):
+        forced = np.unique(np.asarray(forced))
+        extra = np.setdiff1d(rng.permutation(n)[:4 * count], forced)[:count - len(forced)]
+        return np.sort(np.concatenate([forced, extra])).astype(np.int64)
+    return pick(forced_rows), pick(forced_cols)
 
 
-def _check(torch, precision, a, b, c, n, rows, cols, col_base=0):
+def _check(torch, precision, a, b, c, n, rows, cols):
     """Compares C(rows x cols) with fp64 dot products. Only the sampled rows of A and columns of B leave the GPU."""
     r_t = torch.from_numpy(rows).cuda()
     c_t = torch.from_numpy(cols).cuda()
@@ -45,7 +48,7 @@ def _check(torch, precision, a, b, c, n, rows, cols, col_base=0):
     # A is n x n column-major: row i is the strided set {i + l*n}; B's column j is contiguous
     a_rows = a[(r_t[:, None] + k_idx[None, :] * n).reshape(-1)].cpu().numpy().reshape(len(rows), n)
     b_cols = b[(c_t[:, None] * n + k_idx[None, :]).reshape(-1)].cpu().numpy().reshape(len(cols), n)
-    got = c[((c_t[None, :] - col_base) * n + r_t[:, None]).reshape(-1)].cpu().numpy().astype(np.float64)
+    got = c[(c_t[None, :] * n + r_t[:, None]).reshape(-1)].cpu().numpy().astype(np.float64)
     # the compact operands as a small column-major problem: A_s is len(rows) x n (row-contiguous here, so it is passed
     # as a transposed operand), B_s is n x len(cols)
     rr, cc = np.meshgrid(np.arange(len(rows)), np.arange(len(cols)), indexing="ij")
@@ -80,15 +83,16 @@ def test_config5_full_product_and_last_rank_shard(cuda, precision, n):
         assert not bool(torch.isnan(c[s0:s0 + step]).any()), "C keeps poisoned entries"
     rng = np.random.default_rng(n)
     rows, cols = _sample_grid(rng, n, (0, 1, 127, 128, n - 129, n - 2, n - 1), (0, 255, 256, n - 257, n - 256, n - 2, n - 1))
-    assert int(cols[-1]) * n + int(rows[-1]) >= (1 << 31)
+    last = int(cols[-1]) * n + int(rows[-1])            # element index of the last sample
+    assert last == n * n - 1 and last * elem >= (1 << 32)   # byte offsets beyond 32 bits in both cases
     if precision == 32:
-        assert int(cols[-1]) * n + int(rows[-1]) >= (1 << 32) - n
+        assert last >= (1 << 32) - n                        # and element indices that no 32-bit integer holds
     _check(torch, precision, a, b, c, n, rows, cols)
 
     # rank 7 of 8: its column block through the offset arguments, into a fresh C of the block's size
     from clblast_b200.multi_gpu import column_shard
     shard = column_shard(n, 0, n, 0, n, 8, 7)
-    assert shard.n == n // 8 and shard.b_offset == shard.j0 * n >= (1 << 31)
+    assert shard.n == n // 8 and shard.b_offset == shard.j0 * n and shard.b_offset * elem >= (1 << 32)
     c.fill_(float("nan"))
     torch.cuda.synchronize()
     assert cb.Gemm(H.COL, H.NO, H.NO, n, shard.n, n, 1.0, a, 0, n, b, shard.b_offset, n, 0.0, c, shard.c_offset,

@@ -68,7 +68,7 @@ def test_static_table_variant_on_evenly_spaced_offsets_reaches_the_tensor_cores(
     torch = cuda
     rng = np.random.default_rng(77)
     stream = torch.cuda.Stream()
-    for m, n, k, batch in ((256, 256, 128, 12), (512, 256, 192, 6)):
+    for m, n, k, batch in ((256, 256, 256, 12), (512, 256, 192, 6)):
         a_offs = [i * m * k for i in range(batch)]
         b_offs = [i * k * n for i in range(batch)]
         c_offs = [i * m * n for i in range(batch)]
