@@ -36,6 +36,28 @@ def lib() -> ctypes.CDLL:
     L.b200blas_gemm_batched_static.argtypes = L.b200blas_gemm_batched.argtypes
     L.b200blas_convgemm.restype = i
     L.b200blas_convgemm.argtypes = [i, i] + [sz] * 13 + [vp, sz, vp, sz, vp, sz, vp, i]
+    for name in ("b200blas_symm", "b200blas_hemm"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [i, i, i, i, sz, sz, vp, vp, sz, sz, vp, sz, sz, vp, vp, sz, sz, vp, i]
+    for name in ("b200blas_syrk", "b200blas_herk"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [i, i, i, i, sz, sz, vp, vp, sz, sz, vp, vp, sz, sz, vp, i]
+    for name in ("b200blas_syr2k", "b200blas_her2k"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [i, i, i, i, sz, sz, vp, vp, sz, sz, vp, sz, sz, vp, vp, sz, sz, vp, i]
+    for name in ("b200blas_trmm", "b200blas_trsm"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [i, i, i, i, i, i, sz, sz, vp, vp, sz, sz, vp, sz, sz, vp, i]
+    L.b200blas_omatcopy.restype = i
+    L.b200blas_omatcopy.argtypes = [i, i, i, sz, sz, vp, vp, sz, sz, vp, sz, sz, vp, i]
+    for name in ("b200blas_im2col", "b200blas_col2im"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [i, i] + [sz] * 11 + [vp, sz, vp, sz, vp, i]
     L.b200blas_gemm_temp_buffer_size.restype = i
     L.b200blas_gemm_temp_buffer_size.argtypes = [i, i, i, i] + [sz] * 9 + [POINTER(sz)]
     L.b200blas_clear_cache.restype = i
@@ -76,7 +98,8 @@ def lib() -> ctypes.CDLL:
 # Every symbol include/b200blas.h declares; tests check that the built library exports all of them.
 C_ABI_SYMBOLS = [
     "b200blas_gemm", "b200blas_gemm_strided_batched", "b200blas_gemm_batched", "b200blas_gemm_batched_static",
-    "b200blas_convgemm",
+    "b200blas_convgemm", "b200blas_symm", "b200blas_hemm", "b200blas_syrk", "b200blas_herk", "b200blas_syr2k",
+    "b200blas_her2k", "b200blas_trmm", "b200blas_trsm", "b200blas_omatcopy", "b200blas_im2col", "b200blas_col2im",
     "b200blas_gemm_temp_buffer_size", "b200blas_clear_cache", "b200blas_fill_cache", "b200blas_override_parameters",
     "b200blas_retrieve_parameters", "b200blas_set_sm_budget", "b200blas_tensor_core_status", "b200blas_ipc_export", "b200blas_ipc_open",
     "b200blas_ipc_close", "b200blas_stream_copy", "b200blas_stream_wait_flag", "b200blas_stream_write_flag", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",

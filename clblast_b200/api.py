@@ -56,6 +56,21 @@ class Transpose(enum.IntEnum):
     kConjugate = 113
 
 
+class Triangle(enum.IntEnum):
+    kUpper = 121
+    kLower = 122
+
+
+class Diagonal(enum.IntEnum):
+    kNonUnit = 131
+    kUnit = 132
+
+
+class Side(enum.IntEnum):
+    kLeft = 141
+    kRight = 142
+
+
 class KernelMode(enum.IntEnum):
     kCrossCorrelation = 151
     kConvolution = 152
@@ -201,6 +216,121 @@ def Convgemm(kernel_mode, channels, height, width, kernel_h, kernel_w, pad_h, pa
         p, int(kernel_mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
         dilation_h, dilation_w, num_kernels, batch_count, _ptr(im_buffer), im_offset, _ptr(kernel_buffer),
         kernel_offset, _ptr(result_buffer), result_offset, sp, is_async))
+
+
+def _real_precision(p: int) -> int:
+    return {3232: 32, 6464: 64}[p]
+
+
+def Symm(layout, side, triangle, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta, c_buffer,
+         c_offset, c_ld, *, precision=None, stream=None, hermitian=False):
+    """C = alpha*A*B + beta*C or alpha*B*A + beta*C with A symmetric (reference: clblast::Symm, clblast_cuda.h:393-398)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    fn = lib().b200blas_hemm if hermitian else lib().b200blas_symm
+    return _status(fn(p, int(layout), int(side), int(triangle), m, n, scalar_bytes(p, alpha), _ptr(a_buffer), a_offset,
+                      a_ld, _ptr(b_buffer), b_offset, b_ld, scalar_bytes(p, beta), _ptr(c_buffer), c_offset, c_ld, sp,
+                      is_async))
+
+
+def Hemm(layout, side, triangle, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta, c_buffer,
+         c_offset, c_ld, *, precision=None, stream=None):
+    """Symm for a hermitian A (reference: clblast::Hemm, clblast_cuda.h:401-406)."""
+    return Symm(layout, side, triangle, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta, c_buffer,
+                c_offset, c_ld, precision=precision, stream=stream, hermitian=True)
+
+
+def Syrk(layout, triangle, a_transpose, n, k, alpha, a_buffer, a_offset, a_ld, beta, c_buffer, c_offset, c_ld, *,
+         precision=None, stream=None):
+    """One triangle of C = alpha*A*A^T + beta*C (reference: clblast::Syrk, clblast_cuda.h:409-413)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_syrk(p, int(layout), int(triangle), int(a_transpose), n, k, scalar_bytes(p, alpha),
+                                       _ptr(a_buffer), a_offset, a_ld, scalar_bytes(p, beta), _ptr(c_buffer), c_offset,
+                                       c_ld, sp, is_async))
+
+
+def Herk(layout, triangle, a_transpose, n, k, alpha, a_buffer, a_offset, a_ld, beta, c_buffer, c_offset, c_ld, *,
+         precision=None, stream=None):
+    """One triangle of C = alpha*A*A^H + beta*C, alpha and beta real (reference: clblast::Herk, clblast_cuda.h:416-420)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    rp = _real_precision(p)
+    return _status(lib().b200blas_herk(p, int(layout), int(triangle), int(a_transpose), n, k, scalar_bytes(rp, alpha),
+                                       _ptr(a_buffer), a_offset, a_ld, scalar_bytes(rp, beta), _ptr(c_buffer), c_offset,
+                                       c_ld, sp, is_async))
+
+
+def Syr2k(layout, triangle, ab_transpose, n, k, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta,
+          c_buffer, c_offset, c_ld, *, precision=None, stream=None):
+    """One triangle of C = alpha*A*B^T + alpha*B*A^T + beta*C (reference: clblast::Syr2k, clblast_cuda.h:423-428)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_syr2k(p, int(layout), int(triangle), int(ab_transpose), n, k, scalar_bytes(p, alpha),
+                                        _ptr(a_buffer), a_offset, a_ld, _ptr(b_buffer), b_offset, b_ld,
+                                        scalar_bytes(p, beta), _ptr(c_buffer), c_offset, c_ld, sp, is_async))
+
+
+def Her2k(layout, triangle, ab_transpose, n, k, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, beta,
+          c_buffer, c_offset, c_ld, *, precision=None, stream=None):
+    """One triangle of C = alpha*A*B^H + conj(alpha)*B*A^H + beta*C, beta real (reference: clblast::Her2k,
+    clblast_cuda.h:431-436)."""
+    p = precision_of(c_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_her2k(p, int(layout), int(triangle), int(ab_transpose), n, k, scalar_bytes(p, alpha),
+                                        _ptr(a_buffer), a_offset, a_ld, _ptr(b_buffer), b_offset, b_ld,
+                                        scalar_bytes(_real_precision(p), beta), _ptr(c_buffer), c_offset, c_ld, sp,
+                                        is_async))
+
+
+def Trmm(layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld,
+         *, precision=None, stream=None):
+    """B = alpha*op(A)*B or alpha*B*op(A), A triangular (reference: clblast::Trmm, clblast_cuda.h:439-443)."""
+    p = precision_of(b_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_trmm(p, int(layout), int(side), int(triangle), int(a_transpose), int(diagonal), m, n,
+                                       scalar_bytes(p, alpha), _ptr(a_buffer), a_offset, a_ld, _ptr(b_buffer), b_offset,
+                                       b_ld, sp, is_async))
+
+
+def Trsm(layout, side, triangle, a_transpose, diagonal, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld,
+         *, precision=None, stream=None):
+    """Solves op(A)*X = alpha*B or X*op(A) = alpha*B; X overwrites B (reference: clblast::Trsm, clblast_cuda.h:446-450)."""
+    p = precision_of(b_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_trsm(p, int(layout), int(side), int(triangle), int(a_transpose), int(diagonal), m, n,
+                                       scalar_bytes(p, alpha), _ptr(a_buffer), a_offset, a_ld, _ptr(b_buffer), b_offset,
+                                       b_ld, sp, is_async))
+
+
+def Omatcopy(layout, a_transpose, m, n, alpha, a_buffer, a_offset, a_ld, b_buffer, b_offset, b_ld, *, precision=None,
+             stream=None):
+    """B = alpha*op(A), out of place (reference: clblast::Omatcopy, clblast_cuda.h:464-467)."""
+    p = precision_of(b_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_omatcopy(p, int(layout), int(a_transpose), m, n, scalar_bytes(p, alpha), _ptr(a_buffer),
+                                           a_offset, a_ld, _ptr(b_buffer), b_offset, b_ld, sp, is_async))
+
+
+def Im2col(kernel_mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dilation_h,
+           dilation_w, im_buffer, im_offset, col_buffer, col_offset, *, precision=None, stream=None):
+    """Column matrix of one image (reference: clblast::Im2col, clblast_cuda.h:470-475)."""
+    p = precision_of(col_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_im2col(p, int(kernel_mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w,
+                                         stride_h, stride_w, dilation_h, dilation_w, _ptr(im_buffer), im_offset,
+                                         _ptr(col_buffer), col_offset, sp, is_async))
+
+
+def Col2im(kernel_mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dilation_h,
+           dilation_w, col_buffer, col_offset, im_buffer, im_offset, *, precision=None, stream=None):
+    """Adds the column entries back to the image pixels they came from (reference: clblast::Col2im,
+    clblast_cuda.h:478-483)."""
+    p = precision_of(im_buffer, precision)
+    sp, is_async = _stream_arg(stream)
+    return _status(lib().b200blas_col2im(p, int(kernel_mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w,
+                                         stride_h, stride_w, dilation_h, dilation_w, _ptr(col_buffer), col_offset,
+                                         _ptr(im_buffer), im_offset, sp, is_async))
 
 
 def GemmTempBufferSize(layout, a_transpose, b_transpose, m, n, k, a_offset, a_ld, b_offset, b_ld, c_offset, c_ld, *,

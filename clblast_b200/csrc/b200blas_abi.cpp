@@ -24,40 +24,19 @@
 #include "noalloc_bridge.h"
 #include "params_store.h"
 #include "runtime_state.h"
+#include "host_common.h"
 
 namespace b200 {
-
-namespace {
-
-// CLBlast status codes used on this path (include/clblast_cuda.h:40-83 of the reference).
-enum Status : int {
-  kSuccess = 0,
-  kNotImplemented = -1024,
-  kInvalidMatrixA = -1022,
-  kInvalidMatrixB = -1021,
-  kInvalidMatrixC = -1020,
-  kInvalidDimension = -1017,
-  kInvalidLeadDimA = -1016,
-  kInvalidLeadDimB = -1015,
-  kInvalidLeadDimC = -1014,
-  kInsufficientMemoryA = -1011,
-  kInsufficientMemoryB = -1010,
-  kInsufficientMemoryC = -1009,
-  kInvalidBatchCount = -2049,
-  kUnexpectedError = -2039,
-};
 
 // Upper bound on batch_count of the offset-table form: the staged tables take 56 bytes per batch, so this is 3.5 GB
 // of tables; anything larger is a corrupt argument rather than a workload.
 constexpr size_t kMaxBatchCount = size_t(1) << 26;
 
-constexpr int kRowMajor = 101, kColMajor = 102;
-constexpr int kNo = 111, kYes = 112, kConjugate = 113;
-constexpr int kCrossCorrelation = 151, kConvolution = 152;
-
+namespace {
 std::atomic<uint64_t> g_launches{0};
 std::atomic<int> g_sm_budget{0};
 thread_local const char* t_last_kernel = "none";
+}  // namespace
 
 size_t dtype_size(int dtype) {
   switch (dtype) {
@@ -140,11 +119,6 @@ int test_matrix(size_t one, size_t two, const void* buf, size_t offset, size_t l
   if (have < required) return too_small;
   return kSuccess;
 }
-
-struct Extents {
-  size_t a_one, a_two, b_one, b_two, c_one, c_two;
-  bool a_rotated, b_rotated, c_rotated;
-};
 
 // Which dimension of each stored matrix is contiguous (reference: xgemm.hpp:87-107).
 Extents extents(int layout, int ta, int tb, size_t m, size_t n, size_t k) {
@@ -249,8 +223,6 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   return err;
 }
 
-int tensor_core_status(int async);
-
 // Runs `d` either synchronously on the private stream or asynchronously on the caller's stream.
 int run(const GemmDesc& d, void* stream, int async) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -271,7 +243,7 @@ int run(const GemmDesc& d, void* stream, int async) {
 // (mapped host memory, so this is a plain read after the stream synchronisation the call has just done) instead of
 // hanging or trapping. Asynchronous callers read it with b200blas_tensor_core_status once their stream has finished.
 int tensor_core_status(int async) {
-  if (!async && std::strncmp(t_last_kernel, "tc_", 3) == 0) {
+  if (!async) {
     unsigned int status[4] = {0, 0, 0, 0};
     if (tc_status_read(status, true) && status[0] != 0) {
       std::fprintf(stderr, "b200blas: tensor-core kernel gave up waiting (code %u, block %u)\n", status[0], status[1]);
@@ -287,8 +259,6 @@ bool force_small_family(int dtype, size_t m, size_t n, size_t k) {
   const long double lim = static_cast<long double>(t) * t * t;
   return static_cast<long double>(m) * n * k < lim;
 }
-
-}  // namespace
 
 int sm_budget() { return g_sm_budget.load(std::memory_order_relaxed); }
 
@@ -399,15 +369,11 @@ cudaError_t dispatch_desc(const GemmDesc& d, cudaStream_t stream) { return dispa
 
 int status_after_sync() { return tensor_core_status(0); }
 
-}  // namespace b200
-
-using namespace b200;
-
-extern "C" int b200blas_gemm(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k, const void* alpha,
-                             const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld,
-                             const void* beta, void* c, size_t c_offset, size_t c_ld, void* stream, int async) {
+int gemm_validate(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k, const void* a, size_t a_offset,
+                  size_t a_ld, const void* b, size_t b_offset, size_t b_ld, const void* c, size_t c_offset,
+                  size_t c_ld) {
   const size_t elem = dtype_size(dtype);
-  if (elem == 0 || !valid_enums(layout, ta, tb) || !alpha || !beta) return kUnexpectedError;
+  if (elem == 0 || !valid_enums(layout, ta, tb)) return kUnexpectedError;
   if (m == 0 || n == 0 || k == 0) return kInvalidDimension;
   const Extents e = extents(layout, ta, tb, m, n, k);
   int st = test_matrix(e.a_one, e.a_two, a, a_offset, a_ld, elem, true, kInvalidLeadDimA, kInsufficientMemoryA,
@@ -416,10 +382,17 @@ extern "C" int b200blas_gemm(int dtype, int layout, int ta, int tb, size_t m, si
   st = test_matrix(e.b_one, e.b_two, b, b_offset, b_ld, elem, true, kInvalidLeadDimB, kInsufficientMemoryB,
                    kInvalidMatrixB);
   if (st) return st;
-  st = test_matrix(e.c_one, e.c_two, c, c_offset, c_ld, elem, true, kInvalidLeadDimC, kInsufficientMemoryC,
-                   kInvalidMatrixC);
-  if (st) return st;
+  return test_matrix(e.c_one, e.c_two, c, c_offset, c_ld, elem, true, kInvalidLeadDimC, kInsufficientMemoryC,
+                     kInvalidMatrixC);
+}
 
+int gemm_enqueue(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k, const double alpha[2],
+                 const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld,
+                 const double beta[2], void* c, size_t c_offset, size_t c_ld, cudaStream_t stream, int tri,
+                 int real_diag) {
+  if (dtype_size(dtype) == 0 || !valid_enums(layout, ta, tb)) return kUnexpectedError;
+  if (m == 0 || n == 0 || k == 0) return kInvalidDimension;
+  const Extents e = extents(layout, ta, tb, m, n, k);
   GemmDesc d = {};
   d.dtype = dtype;
   normalise(d, layout, ta, tb, m, n, k, a, a_ld, b, b_ld, c, c_ld, e);
@@ -428,10 +401,54 @@ extern "C" int b200blas_gemm(int dtype, int layout, int ta, int tb, size_t m, si
   d.b_off = static_cast<long long>(swapped ? a_offset : b_offset);
   d.c_off = static_cast<long long>(c_offset);
   d.batch = 1;
-  read_scalar(dtype, alpha, 0, d.alpha);
-  read_scalar(dtype, beta, 0, d.beta);
+  d.alpha[0] = alpha[0]; d.alpha[1] = alpha[1];
+  d.beta[0] = beta[0]; d.beta[1] = beta[1];
   d.force_small = force_small_family(dtype, m, n, k);
-  return run(d, stream, async);
+  // The triangle is given for C as the caller sees it; the kernels see the normalised (column-major) C, which for a
+  // row-major call is the transpose.
+  d.tri = tri == 0 ? 0 : ((tri == kUpper) != swapped ? 1 : 2);
+  d.real_diag = real_diag;
+  const cudaError_t err = dispatch(d, stream);
+  if (err != cudaSuccess) {
+    std::fprintf(stderr, "b200blas: CUDA error %d (%s)\n", static_cast<int>(err), cudaGetErrorString(err));
+    return static_cast<int>(err);
+  }
+  return kSuccess;
+}
+
+int begin_call(void* stream, int async, cudaStream_t* out) {
+  *out = static_cast<cudaStream_t>(stream);
+  return async ? 0 : private_stream(out);
+}
+
+int end_call(cudaStream_t stream, int async, cudaError_t err) {
+  if (err == cudaSuccess && !async) err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) {
+    std::fprintf(stderr, "b200blas: CUDA error %d (%s)\n", static_cast<int>(err), cudaGetErrorString(err));
+    return static_cast<int>(err);
+  }
+  return tensor_core_status(async);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200blas_gemm(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k, const void* alpha,
+                             const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld,
+                             const void* beta, void* c, size_t c_offset, size_t c_ld, void* stream, int async) {
+  if (dtype_size(dtype) == 0 || !alpha || !beta) return kUnexpectedError;
+  double al[2], be[2];
+  read_scalar(dtype, alpha, 0, al);
+  read_scalar(dtype, beta, 0, be);
+  int st = gemm_validate(dtype, layout, ta, tb, m, n, k, a, a_offset, a_ld, b, b_offset, b_ld, c, c_offset, c_ld);
+  if (st != kSuccess) return st;
+  cudaStream_t s;
+  const int r = begin_call(stream, async, &s);
+  if (r != 0) return r;
+  st = gemm_enqueue(dtype, layout, ta, tb, m, n, k, al, a, a_offset, a_ld, b, b_offset, b_ld, be, c, c_offset, c_ld, s);
+  if (st != kSuccess) return st;
+  return end_call(s, async, cudaSuccess);
 }
 
 extern "C" int b200blas_gemm_strided_batched(int dtype, int layout, int ta, int tb, size_t m, size_t n, size_t k,

@@ -38,6 +38,12 @@ struct GemmDesc {
   int force_small;                // selection-table override: use the small-tile family
   int tables_aligned4;            // every entry of the per-batch offset tables is a multiple of 4 elements
   int uniform_strides;            // the offset tables are evenly spaced: a_off / a_stride etc. describe them too
+  // Rank-k updates (Syrk, Herk, Syr2k, Her2k) only write one triangle of the square C: 0 = all of C, 1 = elements
+  // with row <= column of the normalised (M-contiguous) C, 2 = elements with row >= column. Tiles wholly outside
+  // the triangle are not computed (reference: XgemmUpper / XgemmLower, src/kernels/level3/xgemm_part4.opencl:23-95,
+  // and the masked write-back of src/kernels/level3/copy_pad.opencl:100-105).
+  int tri;
+  int real_diag;                  // Herk / Her2k: the imaginary part of the diagonal of C is set to zero
 };
 
 }  // namespace b200

@@ -167,7 +167,7 @@ cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 64 || d.is_conv || d.force_small) return cudaErrorNotSupported;
+  if (d.dtype != 64 || d.is_conv || d.force_small || d.tri) return cudaErrorNotSupported;
   static const bool forced_dfma = [] {
     const char* v = std::getenv("B200BLAS_DGEMM");
     return v != nullptr && std::strcmp(v, "dfma") == 0;

@@ -41,6 +41,7 @@ struct SimtParams {
   long long batch;
   long long tiles_m, tiles_n, total_tiles;
   int conj_a, conj_b;
+  int tri, real_diag;  // triangle mask and real diagonal of the rank-k updates (see GemmDesc)
   ConvGeom conv;
 };
 
@@ -55,6 +56,7 @@ struct TraitsF32 {
   static __device__ __forceinline__ T st(S v) { return v; }
   static __device__ __forceinline__ S zero() { return 0.f; }
   static __device__ __forceinline__ S conj(S v) { return v; }
+  static __device__ __forceinline__ S real_only(S v) { return v; }
   static __device__ __forceinline__ void mad(S& c, S a, S b) { c = fmaf(a, b, c); }
   static __device__ __forceinline__ S mul(S a, S b) { return __fmul_rn(a, b); }
   // alpha*x + beta*y as fma(beta, y, alpha*x): the fused form of the reference's AXPBY, bit-identical to the
@@ -73,6 +75,7 @@ struct TraitsF64 {
   static __device__ __forceinline__ T st(S v) { return v; }
   static __device__ __forceinline__ S zero() { return 0.0; }
   static __device__ __forceinline__ S conj(S v) { return v; }
+  static __device__ __forceinline__ S real_only(S v) { return v; }
   static __device__ __forceinline__ void mad(S& c, S a, S b) { c = fma(a, b, c); }
   static __device__ __forceinline__ S mul(S a, S b) { return __dmul_rn(a, b); }
   static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return fma(be, y, __dmul_rn(al, x)); }
@@ -89,6 +92,7 @@ struct TraitsF16 {
   static __device__ __forceinline__ T st(S v) { return __float2half_rn(v); }
   static __device__ __forceinline__ S zero() { return 0.f; }
   static __device__ __forceinline__ S conj(S v) { return v; }
+  static __device__ __forceinline__ S real_only(S v) { return v; }
   static __device__ __forceinline__ void mad(S& c, S a, S b) { c = fmaf(a, b, c); }
   static __device__ __forceinline__ S mul(S a, S b) { return a * b; }
   static __device__ __forceinline__ S axpby(S al, S x, S be, S y) { return al * x + be * y; }
@@ -105,6 +109,7 @@ struct TraitsC32 {
   static __device__ __forceinline__ T st(S v) { return v; }
   static __device__ __forceinline__ S zero() { return make_float2(0.f, 0.f); }
   static __device__ __forceinline__ S conj(S v) { return make_float2(v.x, -v.y); }
+  static __device__ __forceinline__ S real_only(S v) { return make_float2(v.x, 0.f); }
   static __device__ __forceinline__ void mad(S& c, S a, S b) {
     c.x = fmaf(a.x, b.x, c.x);
     c.x = fmaf(-a.y, b.y, c.x);
@@ -129,6 +134,7 @@ struct TraitsC64 {
   static __device__ __forceinline__ T st(S v) { return v; }
   static __device__ __forceinline__ S zero() { return make_double2(0.0, 0.0); }
   static __device__ __forceinline__ S conj(S v) { return make_double2(v.x, -v.y); }
+  static __device__ __forceinline__ S real_only(S v) { return make_double2(v.x, 0.0); }
   static __device__ __forceinline__ void mad(S& c, S a, S b) {
     c.x = fma(a.x, b.x, c.x);
     c.x = fma(-a.y, b.y, c.x);
@@ -344,7 +350,12 @@ gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
     const long long tn = rest % p.tiles_n;
     const long long bz = rest / p.tiles_n;
     const long long m0 = tm * BM, n0 = tn * BN;
-    const long long m_rem = p.m - m0, n_rem = active ? p.n - n0 : 0;  // n_rem == 0 masks every store
+    // A tile wholly outside the triangle of a rank-k update is not computed when the CTA owns a single tile (the
+    // branch is then uniform over the CTA); in a CTA of several tiles it is computed and all its stores are masked.
+    const bool outside = (p.tri == 1 && m0 > n0 + BN - 1) || (p.tri == 2 && n0 > m0 + BM - 1);
+    if (GROUPS == 1 && outside) continue;
+    const long long m_rem = p.m - m0, n_rem = (active && !outside) ? p.n - n0 : 0;  // n_rem == 0 masks every store
+    const bool on_diagonal = p.tri != 0 && m0 < n0 + BN && n0 < m0 + BM;  // element-wise mask needed
 
     const T* a_base = static_cast<const T*>(p.a) + (p.a_offs ? p.a_offs[bz] : p.a_off + bz * p.a_stride);
     const T* b_base = static_cast<const T*>(p.b) + (p.b_offs ? p.b_offs[bz] : p.b_off + bz * p.b_stride);
@@ -431,7 +442,7 @@ gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
 #pragma unroll
         for (int cm = 0; cm < NCM; ++cm) {
           const int mm = cm * (BM / NCM) + tx * CWM;
-          if (c_vec_ok && mm + CWM <= m_rem) {
+          if (c_vec_ok && !on_diagonal && mm + CWM <= m_rem) {
             VecOf<T, CWM> out;
             if (use_beta) {
               const VecOf<T, CWM> old = *reinterpret_cast<const VecOf<T, CWM>*>(c_col + mm);
@@ -447,9 +458,12 @@ gemm_simt_kernel(const SimtParams<typename Tr::S> p) {
 #pragma unroll
             for (int i = 0; i < CWM; ++i) {
               if (mm + i < m_rem) {
+                const long long gi = m0 + mm + i, gj = n0 + nn;
+                if (on_diagonal && (p.tri == 1 ? gi > gj : gi < gj)) continue;
                 const S r = acc[cm * CWM + i][cn * CWN + j];
-                c_col[mm + i] = use_beta ? Tr::st(Tr::axpby(alpha, r, beta, Tr::ld(c_col[mm + i])))
-                                         : Tr::st(Tr::mul(alpha, r));
+                S v = use_beta ? Tr::axpby(alpha, r, beta, Tr::ld(c_col[mm + i])) : Tr::mul(alpha, r);
+                if (p.real_diag && gi == gj) v = Tr::real_only(v);
+                c_col[mm + i] = Tr::st(v);
               }
             }
           }
@@ -483,6 +497,7 @@ struct SimtLauncher {
     p.tiles_n = (d.n + BN - 1) / BN;
     p.total_tiles = p.tiles_m * p.tiles_n * d.batch;
     p.conj_a = d.conj_a; p.conj_b = d.conj_b;
+    p.tri = d.tri; p.real_diag = d.real_diag;
     p.conv = d.conv;
     const long long max_grid = 1LL << 30;
     const long long ctas = (p.total_tiles + GROUPS - 1) / GROUPS;

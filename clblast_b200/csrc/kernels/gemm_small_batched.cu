@@ -294,7 +294,7 @@ bool aligned4(long long v) { return (v & 3) == 0; }
 }  // namespace
 
 cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b || d.tri) return cudaErrorNotSupported;
   if (d.batch < 296) return cudaErrorNotSupported;  // fewer than two problems per SM: the generic kernel is fine
   const bool fits_small = d.m <= 32 && d.n <= 32 && d.k <= 32;
   const bool fits_wide = d.m <= 64 && d.n <= 128 && d.k <= 96;

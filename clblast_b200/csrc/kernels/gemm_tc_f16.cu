@@ -285,7 +285,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const C
 }  // namespace
 
 cudaError_t launch_tc_f16(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
+  if (d.dtype != 16 || d.is_conv || d.force_small || d.tri) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
   if (!walk.ok) return cudaErrorNotSupported;
   if (d.m < 128 || d.n < 64 || d.k < 64) return cudaErrorNotSupported;

@@ -315,7 +315,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const C
 }  // namespace
 
 cudaError_t launch_tc_f16_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 16 || d.is_conv || d.force_small) return cudaErrorNotSupported;
+  if (d.dtype != 16 || d.is_conv || d.force_small || d.tri) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
   if (!walk.ok) return cudaErrorNotSupported;
   // B200BLAS_HGEMM=single keeps the one-CTA-per-tile kernel

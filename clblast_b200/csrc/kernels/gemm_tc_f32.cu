@@ -591,7 +591,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
 }  // namespace
 
 cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b || d.tri) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
   if (!walk.ok) return cudaErrorNotSupported;
   // Static selection: the tensor-core path pays off once there are enough 128x256 tiles and K blocks to fill the
@@ -702,7 +702,7 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
 // narrow dimension becomes the MMA's N. Such batches (2048 x 64x128x96 is the typical one) sit on the FP32 ridge of
 // the CUDA cores; on the tensor cores they are bound by HBM traffic alone.
 cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b || d.tri) return cudaErrorNotSupported;
   static const bool forced_ffma = [] {
     const char* v = std::getenv("B200BLAS_SGEMM");
     return v != nullptr && std::strcmp(v, "ffma") == 0;

@@ -383,7 +383,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
 }  // namespace
 
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b || d.tri) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
   if (!walk.ok) return cudaErrorNotSupported;
   // B200BLAS_SGEMM=ffma forces the CUDA-core kernel, =single the one-CTA-per-tile tensor-core kernels

@@ -76,6 +76,76 @@ int b200blas_convgemm(int dtype, int kernel_mode, size_t channels, size_t height
                       size_t im_offset, const void* kernel, size_t kernel_offset, void* result, size_t result_offset,
                       void* stream, int async);
 
+/* ---- level-3 routines built on the GEMM path -------------------------------------------------------------------
+ * `side` 141/142 (left/right), `triangle` 121/122 (upper/lower), `diagonal` 131/132 (non-unit/unit): CLBlast's enum
+ * values. Scratch (a square copy of the triangular operand, a copy of B, inverted diagonal blocks) comes from the
+ * stream-ordered allocator and is released in stream order. */
+
+/* Replace clblast::Symm<T> / Hemm<T>: C = alpha*A*B + beta*C (left) or alpha*B*A + beta*C (right), A symmetric /
+ * hermitian with one triangle stored (include/clblast_cuda.h:393-406, src/clblast_cuda.cpp:1199-1266,
+ * src/routines/level3/xsymm.cpp:33-96, xhemm.cpp:33-96). Hemm: dtype 3232 or 6464. */
+int b200blas_symm(int dtype, int layout, int side, int triangle, size_t m, size_t n, const void* alpha, const void* a,
+                  size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld, const void* beta, void* c,
+                  size_t c_offset, size_t c_ld, void* stream, int async);
+int b200blas_hemm(int dtype, int layout, int side, int triangle, size_t m, size_t n, const void* alpha, const void* a,
+                  size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld, const void* beta, void* c,
+                  size_t c_offset, size_t c_ld, void* stream, int async);
+
+/* Replace clblast::Syrk<T> / Herk<T>: the `triangle` of C = alpha*A*A^T + beta*C (a_transpose 111) or
+ * alpha*A^T*A + beta*C (include/clblast_cuda.h:409-420, src/clblast_cuda.cpp:1269-1327,
+ * src/routines/level3/xsyrk.cpp:51-160, xherk.cpp:51-165). Herk: dtype 3232 / 6464, conjugate transposes, alpha and
+ * beta point to REAL scalars (float / double), the diagonal of C comes out real. */
+int b200blas_syrk(int dtype, int layout, int triangle, int a_transpose, size_t n, size_t k, const void* alpha,
+                  const void* a, size_t a_offset, size_t a_ld, const void* beta, void* c, size_t c_offset, size_t c_ld,
+                  void* stream, int async);
+int b200blas_herk(int dtype, int layout, int triangle, int a_transpose, size_t n, size_t k, const void* alpha,
+                  const void* a, size_t a_offset, size_t a_ld, const void* beta, void* c, size_t c_offset, size_t c_ld,
+                  void* stream, int async);
+
+/* Replace clblast::Syr2k<T> / Her2k<T,U>: the `triangle` of C = alpha*A*B^T + alpha*B*A^T + beta*C, or with both
+ * operands transposed (include/clblast_cuda.h:423-436, src/clblast_cuda.cpp:1330-1397,
+ * src/routines/level3/xsyr2k.cpp:33-50, xher2k.cpp:33-52). Her2k: alpha complex, beta points to a REAL scalar,
+ * C = alpha*A*B^H + conj(alpha)*B*A^H + beta*C. */
+int b200blas_syr2k(int dtype, int layout, int triangle, int ab_transpose, size_t n, size_t k, const void* alpha,
+                   const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld,
+                   const void* beta, void* c, size_t c_offset, size_t c_ld, void* stream, int async);
+int b200blas_her2k(int dtype, int layout, int triangle, int ab_transpose, size_t n, size_t k, const void* alpha,
+                   const void* a, size_t a_offset, size_t a_ld, const void* b, size_t b_offset, size_t b_ld,
+                   const void* beta, void* c, size_t c_offset, size_t c_ld, void* stream, int async);
+
+/* Replaces clblast::Trmm<T>: B = alpha*op(A)*B (left) or alpha*B*op(A) (right), A triangular
+ * (include/clblast_cuda.h:439-443, src/clblast_cuda.cpp:1400-1436, src/routines/level3/xtrmm.cpp:33-110). */
+int b200blas_trmm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m, size_t n,
+                  const void* alpha, const void* a, size_t a_offset, size_t a_ld, void* b, size_t b_offset, size_t b_ld,
+                  void* stream, int async);
+
+/* Replaces clblast::Trsm<T>: solves op(A)*X = alpha*B (left) or X*op(A) = alpha*B (right) for X, which overwrites B
+ * (include/clblast_cuda.h:446-450, src/clblast_cuda.cpp:1439-1471, src/routines/level3/xtrsm.cpp:40-243,
+ * src/routines/levelx/xinvert.cpp:42-150). dtype 32, 64, 3232 or 6464. */
+int b200blas_trsm(int dtype, int layout, int side, int triangle, int a_transpose, int diagonal, size_t m, size_t n,
+                  const void* alpha, const void* a, size_t a_offset, size_t a_ld, void* b, size_t b_offset, size_t b_ld,
+                  void* stream, int async);
+
+/* ---- the copies either side of the GEMM path --------------------------------------------------------------------- */
+
+/* Replaces clblast::Omatcopy<T>: B = alpha*op(A), out of place (include/clblast_cuda.h:464-467,
+ * src/clblast_cuda.cpp:1510-1544, src/routines/levelx/xomatcopy.cpp:45-78). */
+int b200blas_omatcopy(int dtype, int layout, int a_transpose, size_t m, size_t n, const void* alpha, const void* a,
+                      size_t a_offset, size_t a_ld, void* b, size_t b_offset, size_t b_ld, void* stream, int async);
+
+/* Replace clblast::Im2col<T> / Col2im<T> for one image [channels][height][width] and its column matrix
+ * [channels * kernel_h * kernel_w][output_h * output_w] (include/clblast_cuda.h:470-483,
+ * src/clblast_cuda.cpp:1547-1623, src/routines/levelx/xim2col.cpp:38-95, xcol2im.cpp:38-105). Col2im ADDS the
+ * gathered sums to the image, as the reference does. */
+int b200blas_im2col(int dtype, int kernel_mode, size_t channels, size_t height, size_t width, size_t kernel_h,
+                    size_t kernel_w, size_t pad_h, size_t pad_w, size_t stride_h, size_t stride_w, size_t dilation_h,
+                    size_t dilation_w, const void* im, size_t im_offset, void* col, size_t col_offset, void* stream,
+                    int async);
+int b200blas_col2im(int dtype, int kernel_mode, size_t channels, size_t height, size_t width, size_t kernel_h,
+                    size_t kernel_w, size_t pad_h, size_t pad_w, size_t stride_h, size_t stride_w, size_t dilation_h,
+                    size_t dilation_w, const void* col, size_t col_offset, void* im, size_t im_offset, void* stream,
+                    int async);
+
 /* Replaces clblast::GemmTempBufferSize<T> (include/clblast_cuda.h:523-527, src/clblast_cuda.cpp:1818-1843).
  * Validates the dimensions and writes 0: no kernel of this library needs caller scratch. */
 int b200blas_gemm_temp_buffer_size(int dtype, int layout, int a_transpose, int b_transpose, size_t m, size_t n,

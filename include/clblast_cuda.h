@@ -85,6 +85,92 @@ StatusCode Gemm(const Layout layout, const Transpose a_transpose, const Transpos
                 CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
                 const CUdevice device, CUdeviceptr temp_buffer = 0);
 
+// ---- level-3 routines built on the GEMM path (signatures as in the reference's header) ----------------------------
+
+// C = alpha * A * B + beta * C (side left) or alpha * B * A + beta * C, A symmetric with one triangle stored.
+template <typename T>
+StatusCode Symm(const Layout layout, const Side side, const Triangle triangle, const size_t m, const size_t n,
+                const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                const CUdeviceptr b_buffer, const size_t b_offset, const size_t b_ld, const T beta,
+                CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                const CUdevice device);
+
+// The same for a hermitian A (complex types).
+template <typename T>
+StatusCode Hemm(const Layout layout, const Side side, const Triangle triangle, const size_t m, const size_t n,
+                const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                const CUdeviceptr b_buffer, const size_t b_offset, const size_t b_ld, const T beta,
+                CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                const CUdevice device);
+
+// One triangle of C = alpha * A * A^T + beta * C (or A^T * A).
+template <typename T>
+StatusCode Syrk(const Layout layout, const Triangle triangle, const Transpose a_transpose, const size_t n,
+                const size_t k, const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                const T beta, CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                const CUdevice device);
+
+// One triangle of C = alpha * A * A^H + beta * C (or A^H * A); T is the real type, the matrices are complex.
+template <typename T>
+StatusCode Herk(const Layout layout, const Triangle triangle, const Transpose a_transpose, const size_t n,
+                const size_t k, const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                const T beta, CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                const CUdevice device);
+
+// One triangle of C = alpha * A * B^T + alpha * B * A^T + beta * C (or with both operands transposed).
+template <typename T>
+StatusCode Syr2k(const Layout layout, const Triangle triangle, const Transpose ab_transpose, const size_t n,
+                 const size_t k, const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                 const CUdeviceptr b_buffer, const size_t b_offset, const size_t b_ld, const T beta,
+                 CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                 const CUdevice device);
+
+// One triangle of C = alpha * A * B^H + conj(alpha) * B * A^H + beta * C; T complex, U its real type.
+template <typename T, typename U>
+StatusCode Her2k(const Layout layout, const Triangle triangle, const Transpose ab_transpose, const size_t n,
+                 const size_t k, const T alpha, const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld,
+                 const CUdeviceptr b_buffer, const size_t b_offset, const size_t b_ld, const U beta,
+                 CUdeviceptr c_buffer, const size_t c_offset, const size_t c_ld, const CUcontext context,
+                 const CUdevice device);
+
+// B = alpha * op(A) * B (side left) or alpha * B * op(A), A triangular.
+template <typename T>
+StatusCode Trmm(const Layout layout, const Side side, const Triangle triangle, const Transpose a_transpose,
+                const Diagonal diagonal, const size_t m, const size_t n, const T alpha, const CUdeviceptr a_buffer,
+                const size_t a_offset, const size_t a_ld, CUdeviceptr b_buffer, const size_t b_offset,
+                const size_t b_ld, const CUcontext context, const CUdevice device);
+
+// Solves op(A) * X = alpha * B (side left) or X * op(A) = alpha * B; X overwrites B.
+template <typename T>
+StatusCode Trsm(const Layout layout, const Side side, const Triangle triangle, const Transpose a_transpose,
+                const Diagonal diagonal, const size_t m, const size_t n, const T alpha, const CUdeviceptr a_buffer,
+                const size_t a_offset, const size_t a_ld, CUdeviceptr b_buffer, const size_t b_offset,
+                const size_t b_ld, const CUcontext context, const CUdevice device);
+
+// ---- the copies either side of the GEMM path ------------------------------------------------------------------------
+
+// B = alpha * op(A), out of place.
+template <typename T>
+StatusCode Omatcopy(const Layout layout, const Transpose a_transpose, const size_t m, const size_t n, const T alpha,
+                    const CUdeviceptr a_buffer, const size_t a_offset, const size_t a_ld, CUdeviceptr b_buffer,
+                    const size_t b_offset, const size_t b_ld, const CUcontext context, const CUdevice device);
+
+// Column matrix [channels * kernel_h * kernel_w][output_h * output_w] of one image [channels][height][width].
+template <typename T>
+StatusCode Im2col(const KernelMode kernel_mode, const size_t channels, const size_t height, const size_t width,
+                  const size_t kernel_h, const size_t kernel_w, const size_t pad_h, const size_t pad_w,
+                  const size_t stride_h, const size_t stride_w, const size_t dilation_h, const size_t dilation_w,
+                  const CUdeviceptr im_buffer, const size_t im_offset, CUdeviceptr col_buffer, const size_t col_offset,
+                  const CUcontext context, const CUdevice device);
+
+// The adjoint: adds every column entry to the image pixel it was read from.
+template <typename T>
+StatusCode Col2im(const KernelMode kernel_mode, const size_t channels, const size_t height, const size_t width,
+                  const size_t kernel_h, const size_t kernel_w, const size_t pad_h, const size_t pad_w,
+                  const size_t stride_h, const size_t stride_w, const size_t dilation_h, const size_t dilation_w,
+                  const CUdeviceptr col_buffer, const size_t col_offset, CUdeviceptr im_buffer, const size_t im_offset,
+                  const CUcontext context, const CUdevice device);
+
 // Batched NCHW convolution expressed as an implicit GEMM; result[n][co][ho][wo], alpha = 1 and beta = 0.
 template <typename T>
 StatusCode Convgemm(const KernelMode kernel_mode, const size_t channels, const size_t height, const size_t width,

@@ -1,7 +1,7 @@
 """Builds oracle/_ref/libclblast_ref_kernels.so: the reference's own GEMM kernel source, executed on the CPU.
 
 TEST INFRASTRUCTURE ONLY. The reference's device kernels are OpenCL-C kept as C++ raw strings. This script reads
-the files of the direct GEMM and convolution kernels where they lie in the reference tree, takes the text between
+the files of the direct GEMM, convolution, triangle-conversion, im2col and col2im kernels where they lie in the reference tree, takes the text between
 the raw-string markers, and compiles it as C (OpenCL C is a C99 dialect) against oracle/ref_shim.h (work-item ids, barrier, vector types)
 and oracle/ref_driver.inc (launch logic), once per precision; every symbol but the two entry points of each
 precision is made local with objcopy so the five objects link into one shared object. Nothing from the reference is written into the
@@ -31,6 +31,11 @@ KERNEL_FILES = [
     "src/kernels/level3/xgemm_direct_part3.opencl",
     "src/kernels/levelx/xconvgemm_part1.opencl",
     "src/kernels/levelx/xconvgemm_part2.opencl",
+    "src/kernels/level3/convert_symmetric.opencl",
+    "src/kernels/level3/convert_hermitian.opencl",
+    "src/kernels/level3/convert_triangular.opencl",
+    "src/kernels/levelx/im2col.opencl",
+    "src/kernels/levelx/col2im.opencl",
 ]
 PRECISIONS = {16: "p16", 32: "p32", 64: "p64", 3232: "p3232", 6464: "p6464"}
 
@@ -59,7 +64,8 @@ def build(force: bool = False) -> Path | None:
         objs = []
         for precision, tag in PRECISIONS.items():
             parts = [f'#include "{HERE / "ref_shim.h"}"', f"#define PRECISION {precision}",
-                     f"#define REF_PRECISION_TAG {tag}", "#define ROUTINE_CONVGEMM"]
+                     f"#define REF_PRECISION_TAG {tag}", "#define ROUTINE_CONVGEMM", "#define ROUTINE_SYMM",
+                     "#define ROUTINE_HEMM", "#define ROUTINE_TRMM"]
             for f in KERNEL_FILES:
                 if "xconvgemm" in f and precision > 100:
                     continue  # Convgemm has no complex instantiations
@@ -76,6 +82,8 @@ def build(force: bool = False) -> Path | None:
             if res.returncode != 0:
                 raise RuntimeError(f"compiling the reference kernels for precision {precision} failed:\n{res.stderr[-4000:]}")
             keep = ["-G", f"ref_gemm_direct_{tag}"] + (["-G", f"ref_convgemm_{tag}"] if precision < 100 else [])
+            for entry in ("ref_expand_triangle", "ref_im2col", "ref_col2im"):
+                keep += ["-G", f"{entry}_{tag}"]
             res = subprocess.run(["objcopy", *keep, str(obj)], capture_output=True, text=True)
             if res.returncode != 0:
                 raise RuntimeError(f"objcopy failed:\n{res.stderr[-2000:]}")

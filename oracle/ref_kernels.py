@@ -34,6 +34,14 @@ def lib():
             f = getattr(L, f"ref_convgemm_{tag}")
             f.restype = c_int
             f.argtypes = [c_int] * 14 + [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int]
+        for tag in TAGS.values():
+            f = getattr(L, f"ref_expand_triangle_{tag}")
+            f.restype = c_int
+            f.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p]
+            for name in ("ref_im2col", "ref_col2im"):
+                f = getattr(L, f"{name}_{tag}")
+                f.restype = c_int
+                f.argtypes = [c_int] * 12 + [c_void_p, c_int, c_void_p, c_int]
         _lib = L
     return _lib
 
@@ -61,3 +69,31 @@ def convgemm(precision, mode, channels, height, width, kernel_h, kernel_w, pad_h
             num_kernels, batch_count, _vp(im), im_off, _vp(ker), ker_off, _vp(result), result_off)
     assert st == 0
     return result
+
+
+def expand_triangle(precision, kind, layout, triangle, unit, k, a, a_off, a_ld):
+    """Runs the reference's {Symm,Herm,Tria}{Upper,Lower}ToSquared kernel (kind 0, 1, 2) the way Xsymm / Xhemm / Xtrmm
+    choose and launch it; returns the k*k result in the routine's own type."""
+    upper = (triangle == 121) != (layout == 101)
+    out = np.zeros(k * k, dtype=NP_OF[precision])
+    fn = getattr(lib(), f"ref_expand_triangle_{TAGS[precision]}")
+    assert fn(kind, int(upper), int(bool(unit)), k, _vp(a), a_off, a_ld, _vp(out)) == 0
+    return out
+
+
+def im2col(precision, mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+           im, im_off, col, col_off):
+    """Runs the reference's Xim2colKernelNormal / Flip on host buffers, in place on ``col``."""
+    fn = getattr(lib(), f"ref_im2col_{TAGS[precision]}")
+    assert fn(int(mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+              _vp(im), im_off, _vp(col), col_off) == 0
+    return col
+
+
+def col2im(precision, mode, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+           col, col_off, im, im_off):
+    """Runs the reference's Xcol2imKernelNormal / Flip on host buffers, in place on ``im``."""
+    fn = getattr(lib(), f"ref_col2im_{TAGS[precision]}")
+    assert fn(int(mode), channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+              _vp(col), col_off, _vp(im), im_off) == 0
+    return im

@@ -110,3 +110,9 @@ typedef _Float16 half;
 REFSHIM_VECTORS(half)
 REFSHIM_VECTORS(float)
 REFSHIM_VECTORS(double)
+
+/* OpenCL built-ins the im2col / col2im kernels use on ints. */
+static inline int refshim_min(int a, int b) { return a < b ? a : b; }
+static inline int refshim_max(int a, int b) { return a > b ? a : b; }
+#define min(a, b) refshim_min((a), (b))
+#define max(a, b) refshim_max((a), (b))

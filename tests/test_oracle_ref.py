@@ -85,3 +85,51 @@ def test_conv_kernel_larger_than_image():
     oracle.convgemm(32, 151, 2, 2, 2, 3, 3, 0, 0, 1, 1, 2, 2, 3, 2, im, 0, ker, 0, mine, 0)
     ref.convgemm(32, 151, 2, 2, 2, 3, 3, 0, 0, 1, 1, 2, 2, 3, 2, im, 0, ker, 0, theirs, 0)
     assert np.array_equal(mine, theirs)
+
+
+@pytest.mark.parametrize("precision", (16, 32, 64, 3232, 6464))
+def test_triangle_expansion_reproduces_the_reference_convert_kernels(precision):
+    """Symm / Hemm / Trmm first turn the stored triangle into a square matrix; the oracle's expansion must equal what
+    the reference's convert kernels write, element for element (the values are copies, conjugates, zeros and ones)."""
+    rng = np.random.default_rng(11)
+    kinds = (0, 1, 2) if precision > 100 else (0, 2)
+    cases = 0
+    for kind, layout, triangle, unit, (k, off, pad) in itertools.product(kinds, (101, 102), (121, 122), (False, True),
+                                                                         ((7, 0, 0), (64, 10, 3), (33, 3, 1))):
+        if unit and kind != 2:
+            continue
+        ld = k + pad
+        a = rand(rng, precision, off + ld * k)
+        mine = oracle.expand_triangle(precision, kind, layout, triangle, unit, k, a, off, ld)
+        theirs = ref.expand_triangle(precision, kind, layout, triangle, unit, k, a, off, ld)
+        assert np.array_equal(mine.astype(oracle.NP_OF[precision]).view(np.uint8), theirs.view(np.uint8)), \
+            (kind, layout, triangle, unit, k)
+        cases += 1
+    assert cases >= 36
+
+
+@pytest.mark.parametrize("precision", (16, 32, 64, 3232))
+def test_im2col_and_col2im_reproduce_the_reference_kernels(precision):
+    rng = np.random.default_rng(13)
+    i = 0
+    for mode, pad, dil, ksz, stride, ch in itertools.product((151, 152), (0, 1, 2), (1, 2), (1, 3), (1, 2, 3), (1, 2)):
+        h, w = ((7, 8), (8, 5), (13, 9))[i % 3]
+        off = (0, 10)[i % 2]
+        i += 1
+        oh, ow = oracle.conv_output_size(h, w, ksz, ksz + 1, pad, pad, stride, stride, dil, dil)
+        im = rand(rng, precision, off + ch * h * w, -1, 1)
+        col0 = rand(rng, precision, off + ch * ksz * (ksz + 1) * oh * ow, -1, 1)
+        args = (mode, ch, h, w, ksz, ksz + 1, pad, pad, stride, stride, dil, dil)
+        mine = oracle.im2col(*args, im, off, col0, off)
+        theirs = ref.im2col(precision, *args, im, off, col0.copy(), off)
+        assert np.array_equal(mine.view(np.uint8), theirs.view(np.uint8)), ("im2col",) + args
+        # With gcd(stride, dilation) > 1 the reference's col2im kernel starts its pixel lattice one step late when the
+        # padding is zero and runs one step past the last row (src/kernels/levelx/col2im.opencl:48-54 computes
+        # (pad - 1) / gcd + 1 with truncating division and never tests h_index < input_h); its own tests use strides
+        # {1, 3} with dilations {1, 2} and never get there. Those cases are checked against the definition only.
+        if np.gcd(stride, dil) != 1:
+            continue
+        mine = oracle.col2im(*args, col0, off, im, off)
+        theirs = ref.col2im(precision, *args, col0, off, im.copy(), off)
+        assert np.array_equal(mine.view(np.uint8), theirs.view(np.uint8)), ("col2im",) + args
+    assert i == 144
