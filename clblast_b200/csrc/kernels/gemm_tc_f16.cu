@@ -222,6 +222,8 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     e.map_c = &map_c;
     e.staging = staging;
     e.load_bars = bar_base + 192u;
+    e.hint_store = false;
+    e.store_policy = e.hint_store ? l2_policy(1) : 0;
     uint32_t phases = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       int tm, tn;

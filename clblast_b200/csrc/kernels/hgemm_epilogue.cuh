@@ -59,6 +59,8 @@ struct HalfEpilogue {
   uint8_t* staging;     // kStageBuffers * kStageBytes
   uint32_t load_bars;   // kStageBuffers mbarriers (shared-memory address of the first): "old C block has landed"
   int z;                // problem index (third map coordinate)
+  bool hint_store;      // stores carry `store_policy` (results are written once and not read again by this launch)
+  uint64_t store_policy;
 };
 
 // With beta != 0 the old values of a block are brought into the block's staging buffer by a TMA load (whole lines,
@@ -106,7 +108,10 @@ __device__ __forceinline__ bool write_block(const HalfEpilogue& e, const uint32_
     epilogue_barrier();
     if (elected) {
       // a block that starts inside C is clipped by the TMA unit; one that lies wholly below C is not issued at all
-      if (cta_row0 < e.m) tma_store_3d(e.map_c, smem_u32(buf), cta_row0, col, e.z);
+      if (cta_row0 < e.m) {
+        if (e.hint_store) tma_store_3d_hint(e.map_c, smem_u32(buf), cta_row0, col, e.z, e.store_policy);
+        else tma_store_3d(e.map_c, smem_u32(buf), cta_row0, col, e.z);
+      }
       bulk_commit();
       bulk_wait_read<2>();  // the store issued two blocks ago has left its buffer: block s + 2 lands there
       if (use_beta && next_col >= 0) prefetch_old_block(e, stores + 2, cta_row0, next_col);

@@ -72,6 +72,20 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 // Makes generic-proxy shared-memory writes of this thread visible to the async proxy (TMA, tensor cores).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// L2 eviction priority for the lines a TMA load brings in: 0 normal, 1 evict-first (streamed data), 2 evict-last
+// (data other CTAs will ask for again soon).
+__device__ __forceinline__ uint64_t l2_policy(int kind) {
+  uint64_t p;
+  if (kind == 1) {
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  } else if (kind == 2) {
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  } else {
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  }
+  return p;
+}
+
 // Operand maps carry the batch as third coordinate (always 0 for a single problem).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
@@ -186,6 +200,14 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
                "r"(src), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+// The same store with an L2 eviction policy for the lines it writes (see l2_policy).
+__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap* map, uint32_t src, int x, int y, int z,
+                                                  uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y), "r"(z), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until all but the newest `N` bulk groups of this thread have finished READING shared memory.
 template <int N>
@@ -238,20 +260,6 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       :
       : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
-}
-
-// L2 eviction priority for the lines a TMA load brings in: 0 normal, 1 evict-first (streamed data), 2 evict-last
-// (data other CTAs will ask for again soon).
-__device__ __forceinline__ uint64_t l2_policy(int kind) {
-  uint64_t p;
-  if (kind == 1) {
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  } else if (kind == 2) {
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  } else {
-    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-  }
-  return p;
 }
 
 // The same load with an L2 eviction policy attached.

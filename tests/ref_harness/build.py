@@ -2,7 +2,8 @@
 
 The reference's test sources are compiled unmodified from where they lie in the reference tree (nothing is copied):
 its hand-rolled harness (test/correctness/tester.cpp, testblas.cpp, test/test_utilities.cpp), one main per routine
-(xgemm, xgemmbatched, xgemmstridedbatched, xconvgemm, override_parameters, retrieve_parameters) and the two helper
+(the GEMM family, the level-3 routines built on it, Omatcopy, Im2col, Col2im, override_parameters,
+retrieve_parameters) and the two helper
 translation units its tests need (src/utilities/utilities.cpp, clblast_exceptions.cpp). They are compiled with
 -DCUDA_API against the reference's unmodified include/clblast_cuda.h and linked against THIS repository's
 libclblast.so, so they exercise the drop-in boundary exactly as a user program would. Two stand-ins make that possible:
@@ -33,6 +34,17 @@ PROGRAMS = {
     "xgemmbatched": "test/correctness/routines/levelx/xgemmbatched.cpp",
     "xgemmstridedbatched": "test/correctness/routines/levelx/xgemmstridedbatched.cpp",
     "xconvgemm": "test/correctness/routines/levelx/xconvgemm.cpp",
+    "xsymm": "test/correctness/routines/level3/xsymm.cpp",
+    "xhemm": "test/correctness/routines/level3/xhemm.cpp",
+    "xsyrk": "test/correctness/routines/level3/xsyrk.cpp",
+    "xherk": "test/correctness/routines/level3/xherk.cpp",
+    "xsyr2k": "test/correctness/routines/level3/xsyr2k.cpp",
+    "xher2k": "test/correctness/routines/level3/xher2k.cpp",
+    "xtrmm": "test/correctness/routines/level3/xtrmm.cpp",
+    "xtrsm": "test/correctness/routines/level3/xtrsm.cpp",
+    "xomatcopy": "test/correctness/routines/levelx/xomatcopy.cpp",
+    "xim2col": "test/correctness/routines/levelx/xim2col.cpp",
+    "xcol2im": "test/correctness/routines/levelx/xcol2im.cpp",
     "override_parameters": "test/correctness/misc/override_parameters.cpp",
     "retrieve_parameters": "test/correctness/misc/retrieve_parameters.cpp",
 }

@@ -11,7 +11,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 BUILD = Path(__file__).resolve().parent / "ref_harness" / "_build"
-PROGRAMS = ("xgemm", "xgemmbatched", "xgemmstridedbatched", "xconvgemm", "override_parameters", "retrieve_parameters")
+PROGRAMS = ("xgemm", "xgemmbatched", "xgemmstridedbatched", "xconvgemm", "xsymm", "xhemm", "xsyrk", "xherk", "xsyr2k",
+            "xher2k", "xtrmm", "xtrsm", "xomatcopy", "xim2col", "xcol2im", "override_parameters", "retrieve_parameters")
 
 
 @pytest.mark.parametrize("name", PROGRAMS)
