@@ -194,7 +194,7 @@ def omatcopy(precision, layout, trans, m, n, alpha, a, a_off, a_ld, b, b_off, b_
     if trans == 113:
         src = np.conj(src)
     if precision == 16:
-        res = (np.float32(alpha) * src.astype(np.float32)).astype(np.float16)
+        res = (np.float32(np.float16(alpha)) * src.astype(np.float32)).astype(np.float16)   # alpha arrives as a half
     else:
         res = (NP_OF[precision](alpha) * src).astype(NP_OF[precision])
     for r in range(res.shape[0]):

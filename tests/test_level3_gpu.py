@@ -186,22 +186,27 @@ def test_large_trsm_and_syrk_reach_the_tensor_cores(cuda):
     assert cb.Syrk(H.COL, LOWER, H.NO, n, n, 1.0, b, 0, n, 0.0, c, 0, n) == 0
     B = b.view(n, n).T.double()
     want = torch.tril(B @ B.T)
-    assert ((torch.tril(c.view(n, n).T.double()) - want).abs().max() / n).item() < 2.0 ** -20
+    # k-ascending fp32 accumulation of 2048 terms (the diagonal sums squares, all of one sign): 2^-18 of sum |a||b|
+    assert ((torch.tril(c.view(n, n).T.double()) - want).abs().max() / n).item() < 2.0 ** -18
     assert float(torch.triu(c.view(n, n).T, 1).abs().max()) == 0.0   # the other triangle is untouched
 
 
 def test_argument_checks_follow_the_reference_order(cuda):
+    from tests.test_errors_gpu import RawAlloc
     torch = cuda
     buf = torch.zeros(64 * 64, device="cuda")
-    small = torch.zeros(8, device="cuda")
+    raw = RawAlloc(8 * 4)      # cudaMalloc'ed, so the allocation really ends after 8 floats
+    small = int(raw.ptr)
     S = cb.StatusCode
+    kw = dict(precision=32)
     assert cb.Symm(H.COL, LEFT, UPPER, 0, 4, 1.0, buf, 0, 4, buf, 0, 4, 0.0, buf, 0, 4) == S.kInvalidDimension
     assert cb.Symm(H.COL, LEFT, UPPER, 8, 8, 1.0, buf, 0, 7, buf, 0, 8, 0.0, buf, 0, 8) == S.kInvalidLeadDimA
     assert cb.Symm(H.COL, LEFT, UPPER, 8, 8, 1.0, buf, 0, 8, buf, 0, 7, 0.0, buf, 0, 8) == S.kInvalidLeadDimB
-    assert cb.Symm(H.COL, LEFT, UPPER, 8, 8, 1.0, buf, 0, 8, buf, 0, 8, 0.0, small, 0, 8) == S.kInsufficientMemoryC
+    assert cb.Symm(H.COL, LEFT, UPPER, 8, 8, 1.0, buf, 0, 8, buf, 0, 8, 0.0, small, 0, 8, **kw) == S.kInsufficientMemoryC
     assert cb.Syrk(H.COL, UPPER, H.NO, 8, 0, 1.0, buf, 0, 8, 0.0, buf, 0, 8) == S.kInvalidDimension
-    assert cb.Syrk(H.COL, UPPER, H.NO, 8, 8, 1.0, small, 0, 8, 0.0, buf, 0, 8) == S.kInsufficientMemoryA
+    assert cb.Syrk(H.COL, UPPER, H.NO, 8, 8, 1.0, small, 0, 8, 0.0, buf, 0, 8, **kw) == S.kInsufficientMemoryA
     assert cb.Syrk(H.COL, UPPER, H.NO, 8, 8, 1.0, buf, 0, 8, 0.0, buf, 0, 7) == S.kInvalidLeadDimC
     assert cb.Trmm(H.COL, LEFT, UPPER, H.NO, NONUNIT, 8, 0, 1.0, buf, 0, 8, buf, 0, 8) == S.kInvalidDimension
-    assert cb.Trsm(H.COL, LEFT, UPPER, H.NO, NONUNIT, 8, 8, 1.0, buf, 0, 8, small, 0, 8) == S.kInsufficientMemoryB
+    assert cb.Trsm(H.COL, LEFT, UPPER, H.NO, NONUNIT, 8, 8, 1.0, buf, 0, 8, small, 0, 8, **kw) == S.kInsufficientMemoryB
     assert cb.Trsm(H.ROW, LEFT, UPPER, H.NO, NONUNIT, 8, 8, 1.0, buf, 0, 7, buf, 0, 8) == S.kInvalidLeadDimA
+    raw.free()
