@@ -75,20 +75,30 @@ WORKLOADS = {
                                   batch=64, alpha=1.0, beta=0.0, dist="normal0.1", bound="tensor"),
     "sgemm_batched_512x128": dict(kind="strided", precision=32, layout=COL, ta=NO, tb=NO, m=512, n=512, k=512,
                                   batch=128, alpha=1.0, beta=0.0, dist="uniform1", bound="fp32"),
+    # the next rows of the path: complex GEMM on the real tensor-core kernels, rank-k update, triangular solve
+    "cgemm_4096": dict(kind="gemm", precision=3232, layout=COL, ta=NO, tb=NO, m=4096, n=4096, k=4096, alpha=1.5,
+                       beta=0.5, dist="uniform1", bound="fp32"),
+    "syrk_8192": dict(kind="syrk", precision=32, layout=COL, n=8192, k=8192, alpha=1.0, beta=0.0, dist="uniform1",
+                      bound="fp32"),
+    "trsm_8192": dict(kind="trsm", precision=32, layout=COL, m=8192, n=8192, alpha=1.0, dist="uniform1", bound="fp32"),
     "conv_56": dict(kind="conv", precision=32, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
                     num_kernels=128, batch=32, bound="fp32"),
 }
 SHARDED_IN_EVERY_RUN = ("dgemm_32768_sharded", "sgemm_65536_sharded")
-TORCH_DT = {16: "float16", 32: "float32", 64: "float64"}
-ELEM = {16: 2, 32: 4, 64: 8}
-DTYPE_NAME = {16: "f16", 32: "f32", 64: "f64"}
+TORCH_DT = {16: "float16", 32: "float32", 64: "float64", 3232: "complex64"}
+ELEM = {16: 2, 32: 4, 64: 8, 3232: 8}
+DTYPE_NAME = {16: "f16", 32: "f32", 64: "f64", 3232: "c32"}
 # ncu summaries whose "`roofline.traffic` for bench.py: <bytes> bytes per launch." line feeds roofline.traffic
 PROFILE_OF = {"hgemm_8192": "hgemm_tc_pair_kernel__hgemm_8192.md"}
 
 
 def flops_of(w, scale_m=1):
     if w["kind"] in ("gemm", "sharded"):
-        return 2.0 * w["m"] * scale_m * w["n"] * w["k"]
+        return (8.0 if w["precision"] > 100 else 2.0) * w["m"] * scale_m * w["n"] * w["k"]
+    if w["kind"] == "syrk":
+        return 1.0 * w["n"] * (w["n"] + 1) * w["k"]       # one triangle of n x n outputs, 2k flops each
+    if w["kind"] == "trsm":
+        return 1.0 * w["m"] * w["m"] * w["n"]             # left side: m^2 n
     if w["kind"] == "strided":
         return 2.0 * w["m"] * w["n"] * w["k"] * w["batch"] * scale_m
     oh = (w["height"] + 2 * w["pad"] - w["dil"] * (w["kh"] - 1) - 1) // w["stride"] + 1
@@ -102,6 +112,10 @@ def min_bytes_of(w):
     if w["kind"] in ("gemm", "sharded"):
         m, n, k = w["m"], w["n"], w["k"]
         return e * (m * k + k * n + m * n * (2 if w["beta"] != 0 else 1))
+    if w["kind"] == "syrk":
+        return e * (w["n"] * w["k"] + w["n"] * (w["n"] + 1) // 2 * (2 if w["beta"] != 0 else 1))
+    if w["kind"] == "trsm":
+        return e * (w["m"] * (w["m"] + 1) // 2 + 2 * w["m"] * w["n"])
     if w["kind"] == "strided":
         m, n, k, b = w["m"], w["n"], w["k"], w["batch"]
         return e * b * (m * k + k * n + m * n * (2 if w["beta"] != 0 else 1))
@@ -189,6 +203,10 @@ def fill_big(torch, count, dt, gen, device, dist_name="uniform1"):
         e0 = min(count, s0 + step_)
         if dist_name == "normal0.1":
             out[s0:e0] = (torch.randn(e0 - s0, generator=gen, device=device, dtype=torch.float32) * 0.1).to(dt)
+        elif dt.is_complex:
+            re = torch.rand(e0 - s0, generator=gen, device=device, dtype=torch.float32) * 2 - 1
+            im = torch.rand(e0 - s0, generator=gen, device=device, dtype=torch.float32) * 2 - 1
+            out[s0:e0] = torch.complex(re, im).to(dt)
         else:
             out[s0:e0] = (torch.rand(e0 - s0, generator=gen, device=device, dtype=torch.float32) * 2 - 1).to(dt)
     return out
@@ -202,6 +220,15 @@ def make_inputs(torch, w, device, seed, rows_scale=1):
     def fill(n):
         return fill_big(torch, n, dt, g, device, w.get("dist", "uniform1"))
 
+    if w["kind"] == "syrk":
+        n, k = w["n"], w["k"]
+        return dict(a=fill(n * k), c=torch.full((n * n,), float("nan"), device=device, dtype=dt))
+    if w["kind"] == "trsm":
+        m, n = w["m"], w["n"]
+        a = fill(m * m) * 0.01                      # small off-diagonal entries, unit-sized diagonal: well conditioned
+        a.view(m, m).diagonal().add_(1.0)
+        b = fill(m * n)
+        return dict(a=a, b=b, b0=b.clone())
     if w["kind"] == "gemm":
         m, n, k = w["m"] * rows_scale, w["n"], w["k"]
         pad = w.get("ld_pad", 0)
@@ -239,6 +266,13 @@ def make_inputs(torch, w, device, seed, rows_scale=1):
 
 def launch(cb, w, t, stream, m_override=None):
     """One step of the workload on `stream` (None = the reference's host-synchronous semantics)."""
+    if w["kind"] == "syrk":
+        return cb.Syrk(w["layout"], 122, NO, w["n"], w["k"], w["alpha"], t["a"], 0, w["n"], w["beta"], t["c"], 0, w["n"],
+                       stream=stream)
+    if w["kind"] == "trsm":
+        t["b"].copy_(t["b0"])     # the solve overwrites B: every step starts from the same right-hand side
+        return cb.Trsm(w["layout"], 141, 122, NO, 131, w["m"], w["n"], w["alpha"], t["a"], 0, w["m"], t["b"], 0, w["m"],
+                       stream=stream)
     if w["kind"] == "gemm":
         m = m_override or w["m"]
         return cb.Gemm(w["layout"], w["ta"], w["tb"], m, w["n"], w["k"], w["alpha"], t["a"], 0, t["a_ld"], t["b"], 0,
@@ -371,7 +405,7 @@ def roofline_of(w, kernel_name, kms, peaks, peak_kind, probed, flops):
         if bound == "tensor":
             peak = float(peaks["bf16_tflops"])
             src = f"{peak_kind} cuBLAS bf16 burst"
-        elif bound == "fp32" and kernel_name.startswith("tc_"):
+        elif bound == "fp32" and "tc_" in kernel_name:
             # error-compensated 3xTF32: three tensor-core products per fp32 product
             bound = "tensor"
             peak = (probed or {}).get("tf32_tflops", 756.0) / 3

@@ -214,8 +214,14 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_tc_f16(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f16(d, stream, &name);
       break;
-    case 3232: err = launch_simt_c32(d, stream, &name); break;
-    case 6464: err = launch_simt_c64(d, stream, &name); break;
+    case 3232:
+      err = launch_complex_on_real(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_simt_c32(d, stream, &name);
+      break;
+    case 6464:
+      err = launch_complex_on_real(d, stream, &name);
+      if (err == cudaErrorNotSupported) err = launch_simt_c64(d, stream, &name);
+      break;
     default: return cudaErrorInvalidValue;
   }
   t_last_kernel = name;

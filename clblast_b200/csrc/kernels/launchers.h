@@ -40,6 +40,10 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
 // cudaErrorNotSupported without launching when the call does not meet its shape and alignment requirements.
 cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, const char** name);
 
+// Large single complex GEMMs as a real product of twice the rows and twice the inner dimension on the kernels above
+// (csrc/complex_on_real.cpp). Same contract as launch_tc_f16.
+cudaError_t launch_complex_on_real(const GemmDesc& d, cudaStream_t stream, const char** name);
+
 // Number of SMs persistent kernels may occupy (0 = all); set through b200blas_set_sm_budget.
 int sm_budget();
 
