@@ -104,3 +104,7 @@ C_ABI_SYMBOLS = [
     "b200blas_retrieve_parameters", "b200blas_set_sm_budget", "b200blas_tensor_core_status", "b200blas_ipc_export", "b200blas_ipc_open",
     "b200blas_ipc_close", "b200blas_stream_copy", "b200blas_stream_wait_flag", "b200blas_stream_write_flag", "b200blas_last_kernel", "b200blas_launch_count", "b200blas_version",
 ]
+
+# Every symbol include/b200blas_c.h and include/b200blas_netlib.h declare.
+C_API_SYMBOLS = ['CLBlastSgemm', 'CLBlastDgemm', 'CLBlastCgemm', 'CLBlastZgemm', 'CLBlastHgemm', 'CLBlastSsymm', 'CLBlastDsymm', 'CLBlastCsymm', 'CLBlastZsymm', 'CLBlastHsymm', 'CLBlastChemm', 'CLBlastZhemm', 'CLBlastSsyrk', 'CLBlastDsyrk', 'CLBlastCsyrk', 'CLBlastZsyrk', 'CLBlastHsyrk', 'CLBlastCherk', 'CLBlastZherk', 'CLBlastSsyr2k', 'CLBlastDsyr2k', 'CLBlastCsyr2k', 'CLBlastZsyr2k', 'CLBlastHsyr2k', 'CLBlastCher2k', 'CLBlastZher2k', 'CLBlastStrmm', 'CLBlastDtrmm', 'CLBlastCtrmm', 'CLBlastZtrmm', 'CLBlastHtrmm', 'CLBlastStrsm', 'CLBlastDtrsm', 'CLBlastCtrsm', 'CLBlastZtrsm', 'CLBlastSomatcopy', 'CLBlastDomatcopy', 'CLBlastComatcopy', 'CLBlastZomatcopy', 'CLBlastHomatcopy', 'CLBlastSim2col', 'CLBlastDim2col', 'CLBlastCim2col', 'CLBlastZim2col', 'CLBlastHim2col', 'CLBlastScol2im', 'CLBlastDcol2im', 'CLBlastCcol2im', 'CLBlastZcol2im', 'CLBlastHcol2im', 'CLBlastSconvgemm', 'CLBlastDconvgemm', 'CLBlastHconvgemm', 'CLBlastSgemmBatched', 'CLBlastDgemmBatched', 'CLBlastCgemmBatched', 'CLBlastZgemmBatched', 'CLBlastHgemmBatched', 'CLBlastSgemmStridedBatched', 'CLBlastDgemmStridedBatched', 'CLBlastCgemmStridedBatched', 'CLBlastZgemmStridedBatched', 'CLBlastHgemmStridedBatched']
+NETLIB_SYMBOLS = ['cblas_sgemm', 'cblas_dgemm', 'cblas_cgemm', 'cblas_zgemm', 'cblas_ssymm', 'cblas_dsymm', 'cblas_csymm', 'cblas_zsymm', 'cblas_chemm', 'cblas_zhemm', 'cblas_ssyrk', 'cblas_dsyrk', 'cblas_csyrk', 'cblas_zsyrk', 'cblas_cherk', 'cblas_zherk', 'cblas_ssyr2k', 'cblas_dsyr2k', 'cblas_csyr2k', 'cblas_zsyr2k', 'cblas_cher2k', 'cblas_zher2k', 'cblas_strmm', 'cblas_dtrmm', 'cblas_ctrmm', 'cblas_ztrmm', 'cblas_strsm', 'cblas_dtrsm', 'cblas_ctrsm', 'cblas_ztrsm', 'cblas_somatcopy', 'cblas_domatcopy', 'cblas_comatcopy', 'cblas_zomatcopy']

@@ -12,6 +12,8 @@
 #include <cuda_runtime_api.h>
 
 #include <atomic>
+#include <chrono>
+#include <cstdlib>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -194,6 +196,36 @@ int current_device() {
 
 // ---- dispatch -----------------------------------------------------------------------------------------
 
+// Per-call log, off unless the environment variable B200BLAS_VERBOSE is set (the reference has a compile-time
+// equivalent, -DVERBOSE: src/routines/common.cpp:69-84 prints every kernel it runs and its time). Level 1 prints one
+// line per kernel launch to stderr; level 2 also waits for the kernel and prints its device time, which serialises
+// the stream and is meant for debugging only.
+int verbose_level() {
+  static const int level = [] {
+    const char* v = std::getenv("B200BLAS_VERBOSE");
+    return v ? std::atoi(v) : 0;
+  }();
+  return level;
+}
+
+void log_launch(const GemmDesc& d, const char* name, cudaError_t err, cudaStream_t stream) {
+  std::fprintf(stderr, "[b200blas] %s dtype=%d m=%lld n=%lld k=%lld batch=%lld a_kcontig=%d b_kcontig=%d tri=%d conv=%d -> %s\n",
+               name, d.dtype, d.m, d.n, d.k, d.batch, d.a_kcontig, d.b_kcontig, d.tri, d.is_conv,
+               err == cudaSuccess ? "enqueued" : cudaGetErrorString(err));
+  if (verbose_level() > 1 && err == cudaSuccess) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return;
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    if (cudaStreamSynchronize(stream) == cudaSuccess) {
+      const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+      std::fprintf(stderr, "[b200blas] %s completed, %.3f ms from launch to completion (host clock)\n", name, ms);
+    }
+  }
+}
+
 cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   const char* name = "none";
   cudaError_t err;
@@ -226,6 +258,7 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
   }
   t_last_kernel = name;
   if (err == cudaSuccess) g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (verbose_level() > 0) log_launch(d, name, err, stream);
   return err;
 }
 

@@ -8,7 +8,7 @@ from pathlib import Path
 import pytest
 
 import clblast_b200 as cb
-from clblast_b200._lib import C_ABI_SYMBOLS, LIB_PATH
+from clblast_b200._lib import C_ABI_SYMBOLS, C_API_SYMBOLS, LIB_PATH, NETLIB_SYMBOLS
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -24,6 +24,40 @@ def test_every_declared_c_symbol_is_exported():
     L = cb.lib()
     for name in declared:
         assert getattr(L, name) is not None
+
+
+def test_c_and_netlib_style_layers_export_every_declared_symbol():
+    c_header = (ROOT / "include" / "b200blas_c.h").read_text()
+    n_header = (ROOT / "include" / "b200blas_netlib.h").read_text()
+    assert set(re.findall(r"CLBlastStatusCode (CLBlast\w+)\(", c_header)) == set(C_API_SYMBOLS)
+    assert set(re.findall(r"void (cblas_\w+)\(", n_header)) == set(NETLIB_SYMBOLS)
+    # the names the reference's C API and Netlib layer give these routines (include/clblast_c.h:885,
+    # include/clblast_netlib_c.h:402)
+    assert "CLBlastSgemm" in C_API_SYMBOLS and "CLBlastZher2k" in C_API_SYMBOLS and "cblas_sgemm" in NETLIB_SYMBOLS
+    L = cb.lib()
+    for name in C_API_SYMBOLS + NETLIB_SYMBOLS:
+        assert getattr(L, name) is not None, name
+    # both headers are plain C
+    for header in ("b200blas_c.h", "b200blas_netlib.h"):
+        src = f'#include "{header}"\nint main(void) {{ return 0; }}\n'
+        res = subprocess.run(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", "-I", str(ROOT / "include"), "-I",
+                              "/usr/local/cuda/include", "-"], input=src, capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+
+
+def test_level3_cxx_symbols_are_exported():
+    out = subprocess.run(["nm", "-D", "--defined-only", str(LIB_PATH)], capture_output=True, text=True, check=True).stdout
+    syms = {line.split()[-1] for line in out.splitlines() if line.strip()}
+    for routine in ("Symm", "Syrk", "Syr2k", "Trmm", "Omatcopy", "Im2col", "Col2im"):
+        for t in ("f", "d", "t", "St7complexIfE", "St7complexIdE"):
+            assert any(s.startswith(f"_ZN7clblast{len(routine)}{routine}I{t}E") for s in syms), (routine, t)
+    for t in ("f", "d", "St7complexIfE", "St7complexIdE"):
+        assert any(s.startswith(f"_ZN7clblast4TrsmI{t}E") for s in syms), t
+    for t in ("St7complexIfE", "St7complexIdE"):
+        assert any(s.startswith(f"_ZN7clblast4HemmI{t}E") for s in syms), t
+    assert any(s.startswith("_ZN7clblast4HerkIfE") for s in syms) and any(s.startswith("_ZN7clblast4HerkIdE") for s in syms)
+    assert any(s.startswith("_ZN7clblast5Her2kISt7complexIfEfE") for s in syms)
+    assert any(s.startswith("_ZN7clblast5Her2kISt7complexIdEdE") for s in syms)
 
 
 def test_cxx_api_symbols_have_the_reference_mangling():
