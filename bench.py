@@ -533,7 +533,10 @@ def reference_on_gpu(timeout_s=240):
     for ln in reversed(res.stdout.splitlines()):
         if ln.startswith("{"):
             try:
-                return json.loads(ln)
+                out = json.loads(ln)
+                if res.stderr.strip():
+                    out["stderr_tail"] = res.stderr.strip()[-400:]
+                return out
             except ValueError:
                 break
     return {"unavailable": f"the reference run exited with {res.returncode}: {(res.stderr or res.stdout)[-300:]}"}
