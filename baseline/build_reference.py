@@ -87,7 +87,7 @@ def build(force: bool = False):
     if jobs or not exe.exists() or exe.stat().st_mtime < driver.stat().st_mtime:
         cmd = ["g++", "-std=c++11", "-O2", f"-I{REFERENCE / 'include'}", f"-I{CUDA / 'include'}", str(driver), "-o", str(exe),
                str(lib), f"-L{CUDA / 'lib64' / 'stubs'}", f"-L{CUDA / 'lib64'}", "-lcuda", "-lnvrtc",
-               "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA / 'lib64'}", "-Wl,--allow-shlib-undefined"]
+               "-ldl", "-rdynamic", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA / 'lib64'}", "-Wl,--allow-shlib-undefined"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"linking run_reference failed:\n{res.stderr[-3000:]}")

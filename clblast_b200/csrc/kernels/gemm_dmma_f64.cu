@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
     const long long tn = in_group / rows;
     const long long m0 = tm * BM, n0 = tn * BN;
     const long long m_rem = p.m - m0, n_rem = p.n - n0;
+    // rank-k updates: tiles wholly outside the triangle are not computed (the branch is uniform over the CTA)
+    if ((p.tri == 1 && m0 > n0 + BN - 1) || (p.tri == 2 && n0 > m0 + BM - 1)) continue;
     const double* a_base = static_cast<const double*>(p.a) + (p.a_offs ? p.a_offs[bz] : p.a_off + bz * p.a_stride);
     const double* b_base = static_cast<const double*>(p.b) + (p.b_offs ? p.b_offs[bz] : p.b_off + bz * p.b_stride);
     double* c_base = static_cast<double*>(p.c) + (p.c_offs ? p.c_offs[bz] : p.c_off + bz * p.c_stride);
@@ -126,7 +128,7 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const long long mm = wm + i * 8 + g;
-          if (mm < m_rem) {
+          if (mm < m_rem && (p.tri == 0 || (p.tri == 1 ? m0 + mm <= n0 + nn : m0 + mm >= n0 + nn))) {
             const double r = acc[i][j][h];
             c_col[mm] = use_beta ? fma(beta, c_col[mm], __dmul_rn(alpha, r)) : __dmul_rn(alpha, r);
           }
@@ -154,6 +156,8 @@ cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
   p.tiles_n = (d.n + BN - 1) / BN;
   p.total_tiles = p.tiles_m * p.tiles_n * d.batch;
   p.conj_a = p.conj_b = 0;
+  p.tri = d.tri;
+  p.real_diag = 0;
   p.conv = d.conv;
   const long long max_grid = 1LL << 30;
   const unsigned grid = static_cast<unsigned>(p.total_tiles < max_grid ? p.total_tiles : max_grid);
@@ -167,7 +171,7 @@ cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 64 || d.is_conv || d.force_small || d.tri) return cudaErrorNotSupported;
+  if (d.dtype != 64 || d.is_conv || d.force_small) return cudaErrorNotSupported;
   static const bool forced_dfma = [] {
     const char* v = std::getenv("B200BLAS_DGEMM");
     return v != nullptr && std::strcmp(v, "dfma") == 0;

@@ -64,9 +64,23 @@ struct PairParams {
   long long c_stride;
   const float* alphas;  // per-problem scalars (offset-table calls), or null
   const float* betas;
+  // Rank-k updates (square C, one problem): 1 keeps the elements with row <= column, 2 those with row >= column.
+  // Only the tiles that touch the triangle exist: they are numbered row by row through the triangle, so every
+  // pair of SMs gets the same number of them.
+  int tri;
 };
 
 __device__ __forceinline__ void tile_coords(const PairParams& p, int tile, int& tm, int& tn) {
+  if (p.tri != 0) {
+    // tile = r (r + 1) / 2 + c with c <= r: (r, c) is (tm, tn) in the lower triangle, (tn, tm) in the upper one
+    int r = static_cast<int>((sqrtf(8.f * static_cast<float>(tile) + 1.f) - 1.f) * 0.5f);
+    while (r * (r + 1) / 2 > tile) --r;
+    while ((r + 1) * (r + 2) / 2 <= tile) ++r;
+    const int c = tile - r * (r + 1) / 2;
+    tm = p.tri == 2 ? r : c;
+    tn = p.tri == 2 ? c : r;
+    return;
+  }
   const int per_group = p.raster_group * p.tiles_n;
   const int group = tile / per_group;
   const int first_m = group * p.raster_group;
@@ -100,7 +114,7 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int tiles_per_problem = p.tiles_m * p.tiles_n;
+  const int tiles_per_problem = p.tri != 0 ? p.tiles_m * (p.tiles_m + 1) / 2 : p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_per_problem * p.batches;
   const int pair_index = blockIdx.x >> 1;
   const int pair_count = gridDim.x >> 1;
@@ -282,7 +296,8 @@ sgemm_3xtf32_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
-            if (col0 + j0 + jj < p.n) {
+            const int col = col0 + j0 + jj;
+            if (col < p.n && (p.tri == 0 || (p.tri == 1 ? row <= col : row >= col))) {
               float v = __fmul_rn(alpha, acc[j0 + jj]);
               if (use_beta) v = fmaf(beta, old[jj], v);
               cptr[static_cast<long long>(j0 + jj) * p.ldc] = v;
@@ -383,9 +398,10 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
 }  // namespace
 
 cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const char** name) {
-  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b || d.tri) return cudaErrorNotSupported;
+  if (d.dtype != 32 || d.is_conv || d.force_small || d.conj_a || d.conj_b) return cudaErrorNotSupported;
   const BatchWalk walk = batch_walk(d);
   if (!walk.ok) return cudaErrorNotSupported;
+  if (d.tri != 0 && (d.m != d.n || walk.batches != 1)) return cudaErrorNotSupported;
   // B200BLAS_SGEMM=ffma forces the CUDA-core kernel, =single the one-CTA-per-tile tensor-core kernels
   static const bool disabled = [] {
     const char* v = std::getenv("B200BLAS_SGEMM");
@@ -417,10 +433,12 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   p.alpha = static_cast<float>(d.alpha[0]);
   p.beta = static_cast<float>(d.beta[0]);
   p.raster_group = 8;
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
+  p.tri = d.tri;
+  const long long tiles = d.tri != 0 ? static_cast<long long>(p.tiles_m) * (p.tiles_m + 1) / 2
+                                     : static_cast<long long>(p.tiles_m) * p.tiles_n * p.batches;
   // Enough 256 x 256 tiles to give every pair of SMs two: below that the 128-wide single-CTA tiles fill the
-  // machine better.
-  if (tiles < sm_count() || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  // machine better. (A rank-k update has no single-CTA tensor-core kernel to fall back to: one tile per pair is enough.)
+  if (tiles < (d.tri != 0 ? sm_count() / 2 : sm_count()) || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
 
   CUtensorMap map_a, map_b;
   if (!encode_operand_map(&map_a, 4, a, d.m, d.k, d.lda, !d.a_kcontig, BM, walk.a_batches, walk.a_stride))

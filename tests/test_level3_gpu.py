@@ -210,3 +210,38 @@ def test_argument_checks_follow_the_reference_order(cuda):
     assert cb.Trsm(H.COL, LEFT, UPPER, H.NO, NONUNIT, 8, 8, 1.0, buf, 0, 8, small, 0, 8, **kw) == S.kInsufficientMemoryB
     assert cb.Trsm(H.ROW, LEFT, UPPER, H.NO, NONUNIT, 8, 8, 1.0, buf, 0, 7, buf, 0, 8) == S.kInvalidLeadDimA
     raw.free()
+
+
+@pytest.mark.parametrize("precision,n,k,kernel", ((32, 3072, 384, "tc_f32_3xtf32_pair"), (64, 1536, 200, "dmma_f64")))
+def test_rank_k_updates_on_the_tensor_core_kernels(cuda, precision, n, k, kernel):
+    """Large Syrk / Syr2k run on the tensor-core GEMM kernels, which number only the tiles that touch the triangle and
+    mask the diagonal tiles; checked against fp64 products on the device, including that the other triangle and the
+    padding between columns keep their old contents."""
+    torch = cuda
+    dt = torch.float32 if precision == 32 else torch.float64
+    g = torch.Generator(device="cuda").manual_seed(n)
+    ldc = n + 4
+    for layout, triangle, trans in itertools.product((H.ROW, H.COL), (UPPER, LOWER), (H.NO, H.YES)):
+        a = (torch.rand(n * k, generator=g, device="cuda", dtype=dt) * 2 - 1)
+        b = (torch.rand(n * k, generator=g, device="cuda", dtype=dt) * 2 - 1)
+        c0 = (torch.rand(ldc * n, generator=g, device="cuda", dtype=dt) * 2 - 1)
+        c = c0.clone()
+        # the stored matrix is n x k when (row-major, not transposed) or (column-major, transposed) is read row by row
+        rows_first = (layout == H.ROW) == (trans == H.NO)
+        a_ld = k if rows_first else n
+        A = a.view(n, k).double() if rows_first else a.view(k, n).double().T       # op(A): n x k
+        B = b.view(n, k).double() if rows_first else b.view(k, n).double().T
+        torch.cuda.synchronize()
+        assert cb.Syr2k(layout, triangle, trans, n, k, 1.5, a, 0, a_ld, b, 0, a_ld, 0.5, c, 0, ldc) == 0
+        assert kernel in cb.last_kernel(), cb.last_kernel()
+        want = 1.5 * (A @ B.T + B @ A.T)
+        C0 = c0.view(n, ldc)[:, :n].double()
+        C = c.view(n, ldc)[:, :n].double()
+        if layout == H.COL:                      # memory rows are columns of C
+            C0, C = C0.T, C.T
+        keep = torch.triu(torch.ones(n, n, dtype=torch.bool, device="cuda")) if triangle == UPPER else \
+            torch.tril(torch.ones(n, n, dtype=torch.bool, device="cuda"))
+        err = ((C - (want + 0.5 * C0)).abs()[keep].max() / (3.0 * k + 0.5)).item()
+        assert err < (2.0 ** -20 if precision == 32 else 2.0 ** -48), err
+        assert torch.equal(C[~keep], C0[~keep])
+        assert torch.equal(c.view(n, ldc)[:, n:], c0.view(n, ldc)[:, n:])
