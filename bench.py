@@ -83,6 +83,11 @@ WORKLOADS = {
     "trsm_8192": dict(kind="trsm", precision=32, layout=COL, m=8192, n=8192, alpha=1.0, dist="uniform1", bound="fp32"),
     "conv_56": dict(kind="conv", precision=32, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
                     num_kernels=128, batch=32, bound="fp32"),
+    # the same convolution in half and double precision: im2col into scratch, then the tensor-core GEMM kernels
+    "hconv_56": dict(kind="conv", precision=16, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
+                     num_kernels=128, batch=32, bound="tensor"),
+    "dconv_56": dict(kind="conv", precision=64, channels=64, height=56, width=56, kh=3, kw=3, pad=1, stride=1, dil=1,
+                     num_kernels=128, batch=32, bound="fp64"),
 }
 SHARDED_IN_EVERY_RUN = ("dgemm_32768_sharded", "sgemm_65536_sharded")
 TORCH_DT = {16: "float16", 32: "float32", 64: "float64", 3232: "complex64"}

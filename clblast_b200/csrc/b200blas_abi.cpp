@@ -238,11 +238,11 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);
       break;
     case 64:
-      err = launch_dmma_f64(d, stream, &name);
+      err = d.is_conv ? launch_conv_two_step(d, stream, &name) : launch_dmma_f64(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f64(d, stream, &name);
       break;
     case 16:
-      err = launch_tc_f16_pair(d, stream, &name);
+      err = d.is_conv ? launch_conv_two_step(d, stream, &name) : launch_tc_f16_pair(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_tc_f16(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f16(d, stream, &name);
       break;

@@ -44,6 +44,10 @@ cudaError_t launch_small_batched_f32(const GemmDesc& d, cudaStream_t stream, con
 // (csrc/complex_on_real.cpp). Same contract as launch_tc_f16.
 cudaError_t launch_complex_on_real(const GemmDesc& d, cudaStream_t stream, const char** name);
 
+// Half / double Convgemm as im2col into scratch plus one strided-batched GEMM on the tensor-core kernels
+// (csrc/conv_two_step.cpp). Same contract as launch_tc_f16.
+cudaError_t launch_conv_two_step(const GemmDesc& d, cudaStream_t stream, const char** name);
+
 // Number of SMs persistent kernels may occupy (0 = all); set through b200blas_set_sm_budget.
 int sm_budget();
 

@@ -248,12 +248,16 @@ __global__ void __launch_bounds__(NB) invert_blocks_kernel(long long k, const T*
 // ---- im2col / col2im ----------------------------------------------------------------------------------------------------
 
 template <typename T>
-__global__ void im2col_kernel(ConvGeom g, int out_h, long long total, const T* __restrict__ im, T* __restrict__ col) {
+__global__ void im2col_kernel(ConvGeom g, int out_h, long long per_image, long long total, const T* __restrict__ im_all,
+                              long long im_stride, T* __restrict__ col) {
   const int khw = g.kernel_h * g.kernel_w;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int wo = static_cast<int>(idx % g.out_w);
-    long long rest = idx / g.out_w;
+    const long long image_index = idx / per_image;   // column matrices of consecutive images follow one another
+    const long long in_image = idx - image_index * per_image;
+    const T* __restrict__ im = im_all + image_index * im_stride;
+    const int wo = static_cast<int>(in_image % g.out_w);
+    long long rest = in_image / g.out_w;
     const int ho = static_cast<int>(rest % out_h);
     rest /= out_h;
     const int kidx = static_cast<int>(rest % khw);
@@ -374,12 +378,14 @@ cudaError_t launch_invert_diagonal_blocks(int dtype, bool mem_upper, bool unit_d
 }
 
 cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* im, long long im_off, void* col,
-                          long long col_off, cudaStream_t stream) {
-  const long long total = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w * out_h * g.out_w;
-  if (total <= 0) return cudaErrorInvalidValue;
+                          long long col_off, cudaStream_t stream, long long images, long long im_stride) {
+  const long long per_image = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w * out_h * g.out_w;
+  const long long total = per_image * images;
+  if (per_image <= 0 || images <= 0) return cudaErrorInvalidValue;
   return by_dtype(dtype, [&](auto* tag) {
     using T = typename std::remove_pointer<decltype(tag)>::type;
-    im2col_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(g, out_h, total, static_cast<const T*>(im) + im_off,
+    im2col_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(g, out_h, per_image, total,
+                                                               static_cast<const T*>(im) + im_off, im_stride,
                                                                static_cast<T*>(col) + col_off);
     return cudaGetLastError();
   });

@@ -31,8 +31,9 @@ cudaError_t launch_invert_diagonal_blocks(int dtype, bool mem_upper, bool unit_d
 
 // col[c][kernel index][ho][wo] = im[c][ho*stride - pad + kh*dil][wo*stride - pad + kw*dil] (zero outside the image),
 // kernel index = kh*KW + kw, mirrored when g.flip. Reference: src/kernels/levelx/im2col.opencl:24-62.
+// `images` > 1: that many images, `im_stride` elements apart; their column matrices follow one another in col.
 cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* im, long long im_off, void* col,
-                          long long col_off, cudaStream_t stream);
+                          long long col_off, cudaStream_t stream, long long images = 1, long long im_stride = 0);
 // im[c][h][w] += sum of the col entries that im2col would have read from that pixel.
 // Reference: src/kernels/levelx/col2im.opencl:29-89.
 cudaError_t launch_col2im(int dtype, const ConvGeom& g, int out_h, const void* col, long long col_off, void* im,

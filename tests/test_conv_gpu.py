@@ -129,3 +129,36 @@ def test_config4_convolution_shape(cuda):
             assert torch.equal(one, full[n * per:(n + 1) * per])
         else:  # one image alone is too small for the tensor-core path: same values to fp32 accuracy, not the same bits
             assert torch.allclose(one, full[n * per:(n + 1) * per], atol=2e-5, rtol=0)
+
+
+@pytest.mark.parametrize("precision", (16, 64))
+def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision):
+    """Large half / double convolutions write the column matrix of a group of images to scratch and multiply it by the
+    weights on the tensor-core GEMM kernels; both kernel modes, stride, dilation and ragged extents against the fp64
+    oracle with the reference's margins."""
+    rng = np.random.default_rng(precision)
+    cases = [
+        # channels, H, W, kh, kw, pad, stride, dil, num_kernels, batch
+        (64, 56, 56, 3, 3, 1, 1, 1, 128, 6),
+        (16, 40, 37, 3, 3, 1, 2, 1, 96, 40),
+        (12, 33, 35, 5, 3, 2, 1, 2, 200, 9),
+    ]
+    for mode, (ch, h, w, kh, kw, pad, stride, dil, nk, batch) in itertools.product((151, 152), cases):
+        oh, ow = oracle.conv_output_size(h, w, kh, kw, pad, pad, stride, stride, dil, dil)
+        im = H.rand_buffer(rng, precision, 5 + batch * ch * h * w, -1, 1)
+        ker = (H.rand_buffer(rng, precision, 3 + nk * ch * kh * kw, -1, 1) * 0.1).astype(H.NP_OF[precision])
+        res = np.full(7 + batch * nk * oh * ow, np.nan, dtype=H.NP_OF[precision])
+        dim, dker, dres = (H.to_device(cuda, precision, x) for x in (im, ker, res))
+        cuda.cuda.synchronize()
+        st = cb.Convgemm(mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, dim, 5, dker, 3, dres, 7,
+                         precision=precision)
+        assert st == cb.StatusCode.kSuccess
+        assert cb.last_kernel().startswith("conv_im2col_"), cb.last_kernel()
+        want = oracle.convgemm(precision, mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, im, 5, ker,
+                               3, np.zeros_like(res), 7, f64=True)
+        got = H.to_host(precision, dres)
+        assert np.isnan(got[:7].astype(np.float64)).all()          # nothing before the offset was touched
+        bad, worst = oracle.count_mismatches(precision, got[7:], want[7:])
+        assert bad == 0, (mode, ch, h, w, worst)
+        k = ch * kh * kw
+        assert worst <= (2e-3 if precision == 16 else 2.0 ** -48 * k), (worst, k)
