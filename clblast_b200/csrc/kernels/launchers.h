@@ -48,6 +48,10 @@ cudaError_t launch_complex_on_real(const GemmDesc& d, cudaStream_t stream, const
 // (csrc/conv_two_step.cpp). Same contract as launch_tc_f16.
 cudaError_t launch_conv_two_step(const GemmDesc& d, cudaStream_t stream, const char** name);
 
+// Large half / single GEMMs with operands TMA cannot address: the offending operands are copied once into scratch with
+// an aligned pitch and the kernels above run on the copies (csrc/repitch.cpp). Same contract as launch_tc_f16.
+cudaError_t launch_repitched(const GemmDesc& d, cudaStream_t stream, const char** name);
+
 // Number of SMs persistent kernels may occupy (0 = all); set through b200blas_set_sm_budget.
 int sm_budget();
 

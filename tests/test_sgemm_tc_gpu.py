@@ -205,3 +205,40 @@ def test_values_next_to_the_largest_finite_float(cuda):
     got = c.cpu().numpy().astype(np.float64).reshape(n, n)
     assert np.isfinite(got).all()
     assert (np.abs(got - want) / mag).max() < 2.0 ** -20
+
+
+@pytest.mark.parametrize("precision", (32, 16))
+def test_large_problems_with_unaligned_operands_are_repitched(cuda, precision):
+    """Operands TMA cannot address (odd leading dimension, base off the 16-byte grid) of a large product are copied once
+    into scratch with an aligned pitch and multiplied by the TMA kernels; every orientation, sampled against exact fp64
+    dot products, padding between the columns of C untouched."""
+    torch = cuda
+    dt = torch.float32 if precision == 32 else torch.float16
+    m, n, k = 2049, 1500, 520
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rs = np.random.default_rng(11)
+    for ta, tb in itertools.product((H.NO, H.YES), repeat=2):
+        a_rows, a_cols = (m, k) if ta == H.NO else (k, m)
+        b_rows, b_cols = (k, n) if tb == H.NO else (n, k)
+        lda, ldb, ldc = a_rows + 3, b_rows + 1, m + 5
+        a_off, b_off = 1, 2
+        a = ((torch.rand(a_off + lda * a_cols, generator=g, device="cuda") * 2 - 1) * 0.5).to(dt)
+        b = ((torch.rand(b_off + ldb * b_cols, generator=g, device="cuda") * 2 - 1) * 0.5).to(dt)
+        c0 = (torch.rand(ldc * n, generator=g, device="cuda") * 2 - 1).to(dt)
+        c = c0.clone()
+        torch.cuda.synchronize()
+        assert cb.Gemm(H.COL, ta, tb, m, n, k, 1.5, a, a_off, lda, b, b_off, ldb, 0.5, c, 0, ldc) == 0
+        assert cb.last_kernel().startswith("repitched_tc_"), cb.last_kernel()
+        rows, cols = rs.integers(0, m, 2048), rs.integers(0, n, 2048)
+        rows[:4], cols[:4] = (0, m - 1, 0, m - 1), (0, 0, n - 1, n - 1)
+        ah, bh = a[a_off:].cpu().numpy().astype(np.float64), b[b_off:].cpu().numpy().astype(np.float64)
+        opa = ah.reshape(a_cols, lda)[:, :a_rows]
+        opa = opa.T if ta == H.NO else opa
+        opb = bh.reshape(b_cols, ldb)[:, :b_rows]
+        opb = opb if tb == H.NO else opb.T
+        old = c0.cpu().numpy().astype(np.float64)[cols * ldc + rows]
+        want = 1.5 * np.einsum("ik,ik->i", opa[rows], opb[cols]) + 0.5 * old
+        mag = 1.5 * np.einsum("ik,ik->i", np.abs(opa[rows]), np.abs(opb[cols])) + 0.5
+        got = c.cpu().numpy().astype(np.float64)[cols * ldc + rows]
+        assert (np.abs(got - want) / mag).max() < (2.0 ** -20 if precision == 32 else 2e-3)
+        assert torch.equal(c.view(n, ldc)[:, m:], c0.view(n, ldc)[:, m:])
