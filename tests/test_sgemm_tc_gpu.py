@@ -101,7 +101,7 @@ def test_config2_ragged_shape(cuda):
         c = c0.clone()
         torch.cuda.synchronize()
         assert cb.Gemm(H.COL, ta, tb, m, n, k, 1.5, a, 0, lda, b, 0, ldb, 0.5, c, 0, ldc) == 0
-        assert cb.last_kernel().startswith("tc_f32"), cb.last_kernel()
+        assert cb.last_kernel().startswith(("tc_f32", "repitched_tc_f32")), cb.last_kernel()
         rows, cols = rs.integers(0, m, 2048), rs.integers(0, n, 2048)
         rows[:4], cols[:4] = (0, m - 1, 0, m - 1), (0, 0, n - 1, n - 1)
         ah, bh = a.cpu().numpy().astype(np.float64), b.cpu().numpy().astype(np.float64)
