@@ -78,6 +78,10 @@ struct Tc32Params {
   long long image_stride, c_stride;
   int batch;
   ConvGeom conv;
+  // Division-free gather (rows of at least eight output pixels, offsets that fit 32 bits): kg / (kernel_h * kernel_w)
+  // and tap / kernel_w become multiply-high by these constants (0: the divisor is 1).
+  int conv_fast;
+  unsigned khw_magic, kw_magic;
 };
 
 template <int BN>
@@ -432,8 +436,56 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         wo0 = p_first - ho0 * p.conv.out_w;
         pixels_left = p.m - p_first;  // <= 0: the whole group lies beyond the image
       }
+      // Fast gather: what depends on the pixel only is computed once per tile. Eight consecutive pixels of rows that
+      // hold at least eight lie on output rows ho0 and ho0 + 1: bit e of row1_mask says which, bit e of live_mask that
+      // pixel e exists; pix_off is the pixel's offset inside a channel plane for tap (0, 0) without padding, pix_w its
+      // column there.
+      int pix_off[CONV ? 8 : 1], pix_w[CONV ? 8 : 1];
+      unsigned row1_mask = 0u, live_mask = 0u;
+      if (CONV && p.conv_fast) {
+        int ho = ho0, wo = wo0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pix_w[e] = wo * p.conv.stride_w;
+          pix_off[e] = ho * p.conv.stride_h * p.conv.width + pix_w[e];
+          if (ho != ho0) row1_mask |= 1u << e;
+          if (e < pixels_left) live_mask |= 1u << e;
+          if (++wo == p.conv.out_w) { wo = 0; ++ho; }
+        }
+      }
       auto gather = [&](int kb) {
         if constexpr (CONV) {
+          if (p.conv_fast) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const unsigned kg = static_cast<unsigned>(kb * BK + kr + 16 * u);
+              const unsigned c_id = p.khw_magic ? __umulhi(kg, p.khw_magic) : kg;
+              const unsigned k2 = kg - c_id * static_cast<unsigned>(khw);
+              unsigned kh_id = p.kw_magic ? __umulhi(k2, p.kw_magic) : k2;
+              unsigned kw_id = k2 - kh_id * static_cast<unsigned>(p.conv.kernel_w);
+              if (p.conv.flip) {
+                kh_id = p.conv.kernel_h - 1 - kh_id;
+                kw_id = p.conv.kernel_w - 1 - kw_id;
+              }
+              const int dh = static_cast<int>(kh_id) * p.conv.dil_h - p.conv.pad_h;
+              const int dw = static_cast<int>(kw_id) * p.conv.dil_w - p.conv.pad_w;
+              const bool row0 = static_cast<unsigned>(ho0 * p.conv.stride_h + dh) < static_cast<unsigned>(p.conv.height);
+              const bool row1 =
+                  static_cast<unsigned>((ho0 + 1) * p.conv.stride_h + dh) < static_cast<unsigned>(p.conv.height);
+              unsigned mask = live_mask & ((row0 ? ~row1_mask : 0u) | (row1 ? row1_mask : 0u));
+              if (kg >= static_cast<unsigned>(p.k)) mask = 0u;
+              // only formed, never read, where the mask or the column test fails
+              const float* base = image + static_cast<long long>(c_id) * p.conv.height * p.conv.width +
+                                  (dh * p.conv.width + dw);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const bool ok = ((mask >> e) & 1u) &&
+                                static_cast<unsigned>(pix_w[e] + dw) < static_cast<unsigned>(p.conv.width);
+                gathered[u][e] = ok ? base[pix_off[e]] : 0.f;
+              }
+            }
+            return;
+          }
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int kg = kb * BK + kr + 16 * u;
@@ -797,6 +849,22 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   p.c_stride = d.c_stride;
   p.batch = static_cast<int>(d.batch);
   p.conv = d.conv;
+  {
+    const long long khw = static_cast<long long>(d.conv.kernel_h) * d.conv.kernel_w;
+    const long long span = (static_cast<long long>(d.conv.height) + 2LL * (d.conv.pad_h > 0 ? d.conv.pad_h : 0) +
+                            d.conv.stride_h + static_cast<long long>(d.conv.kernel_h) * d.conv.dil_h) *
+                               d.conv.width +
+                           static_cast<long long>(d.conv.kernel_w) * d.conv.dil_w + d.conv.pad_w;
+    static const bool slow_gather = [] {
+      const char* v = std::getenv("B200BLAS_CONV_GATHER");
+      return v != nullptr && std::strcmp(v, "general") == 0;
+    }();
+    // multiply-high by ceil(2^32 / d) equals the quotient while dividend * d < 2^32
+    p.conv_fast = !slow_gather && d.conv.out_w >= 8 && (d.k + 64) * khw < (1LL << 32) && khw * d.conv.kernel_w < (1LL << 32) &&
+                  span < (1LL << 31) && d.conv.stride_h > 0 && d.conv.stride_w > 0;
+    p.khw_magic = khw > 1 ? static_cast<unsigned>(((1ULL << 32) + khw - 1) / khw) : 0u;
+    p.kw_magic = d.conv.kernel_w > 1 ? static_cast<unsigned>(((1ULL << 32) + d.conv.kernel_w - 1) / d.conv.kernel_w) : 0u;
+  }
 
   const int device_sms = sm_count();
   if (device_sms <= 0) return cudaErrorNotSupported;

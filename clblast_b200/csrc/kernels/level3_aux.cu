@@ -247,29 +247,45 @@ __global__ void __launch_bounds__(NB) invert_blocks_kernel(long long k, const T*
 
 // ---- im2col / col2im ----------------------------------------------------------------------------------------------------
 
+// One CTA writes kIm2colChunk consecutive elements of one row (channel, kernel index) of one image's column matrix:
+// the row's tap is decoded once per CTA, and each thread walks its output pixels with additions only.
+constexpr int kIm2colChunk = 2048;
 template <typename T>
-__global__ void im2col_kernel(ConvGeom g, int out_h, long long per_image, long long total, const T* __restrict__ im_all,
-                              long long im_stride, T* __restrict__ col) {
+__global__ void __launch_bounds__(256) im2col_kernel(ConvGeom g, int out_h, int plane, int chunks, long long rows,
+                                                     long long images, const T* __restrict__ im_all,
+                                                     long long im_stride, T* __restrict__ col) {
   const int khw = g.kernel_h * g.kernel_w;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long image_index = idx / per_image;   // column matrices of consecutive images follow one another
-    const long long in_image = idx - image_index * per_image;
-    const T* __restrict__ im = im_all + image_index * im_stride;
-    const int wo = static_cast<int>(in_image % g.out_w);
-    long long rest = in_image / g.out_w;
-    const int ho = static_cast<int>(rest % out_h);
-    rest /= out_h;
-    const int kidx = static_cast<int>(rest % khw);
-    const int c = static_cast<int>(rest / khw);
+  const long long units = rows * chunks;  // per image
+  const int step_h = 256 / g.out_w, step_w = 256 - step_h * g.out_w;
+  for (long long unit = blockIdx.x; unit < units * images; unit += gridDim.x) {
+    const long long image_index = unit / units;
+    const long long in_image = unit - image_index * units;
+    const long long row = in_image / chunks;
+    const int chunk = static_cast<int>(in_image - row * chunks);
+    const int c = static_cast<int>(row / khw);
+    const int kidx = static_cast<int>(row - static_cast<long long>(c) * khw);
     const int tap = g.flip ? khw - 1 - kidx : kidx;  // the tap whose value lands at this kernel index
     const int kh = tap / g.kernel_w, kw = tap - kh * g.kernel_w;
-    const int h = ho * g.stride_h - g.pad_h + kh * g.dil_h;
-    const int w = wo * g.stride_w - g.pad_w + kw * g.dil_w;
-    T v = El<T>::zero();
-    if (h >= 0 && h < g.height && w >= 0 && w < g.width)
-      v = im[(static_cast<long long>(c) * g.height + h) * g.width + w];
-    col[idx] = v;
+    const int dh = kh * g.dil_h - g.pad_h, dw = kw * g.dil_w - g.pad_w;
+    const T* __restrict__ im = im_all + image_index * im_stride + static_cast<long long>(c) * g.height * g.width;
+    T* __restrict__ out = col + (image_index * rows + row) * plane;  // column matrices of consecutive images are adjacent
+    int pos = chunk * kIm2colChunk + threadIdx.x;
+    int ho = pos / g.out_w, wo = pos - ho * g.out_w;
+#pragma unroll 4
+    for (int i = 0; i < kIm2colChunk / 256; ++i) {
+      if (pos < plane) {
+        const int h = ho * g.stride_h + dh, w = wo * g.stride_w + dw;
+        T v = El<T>::zero();
+        if (static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
+            static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
+          v = im[static_cast<long long>(h) * g.width + w];
+        out[pos] = v;
+      }
+      pos += 256;
+      ho += step_h;
+      wo += step_w;
+      if (wo >= g.out_w) { wo -= g.out_w; ++ho; }
+    }
   }
 }
 
@@ -311,6 +327,41 @@ unsigned grid_for(long long total, int threads) {
   const long long blocks = (total + threads - 1) / threads;
   const long long cap = static_cast<long long>(sm_count() > 0 ? sm_count() : 1) * 32;
   return static_cast<unsigned>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+// ---- re-pitching copy -------------------------------------------------------------------------------------------------
+
+// One CTA moves one segment of kSegBytes of one line: coalesced element loads from the (arbitrarily aligned) source
+// into shared memory, then 16-byte stores to the aligned destination. Both jobs share the launch.
+constexpr int kSegBytes = 8192;
+struct RepitchParams {
+  RepitchJob job[2];
+  long long segs_per_line[2];
+  long long first_block_of_second;
+};
+
+template <typename W>  // W: an unsigned type of the element's width
+__global__ void __launch_bounds__(256) repitch_kernel(const RepitchParams p) {
+  constexpr int SEG = kSegBytes / static_cast<int>(sizeof(W));
+  constexpr int VEC = 16 / static_cast<int>(sizeof(W));
+  __shared__ __align__(16) W seg[SEG];
+  long long block = blockIdx.x;
+  const int which = block >= p.first_block_of_second ? 1 : 0;
+  if (which) block -= p.first_block_of_second;
+  const RepitchJob& job = p.job[which];
+  const long long line = block / p.segs_per_line[which];
+  const long long x0 = (block - line * p.segs_per_line[which]) * SEG;
+  const W* __restrict__ src = static_cast<const W*>(job.src) + line * job.src_ld + x0;
+  const long long valid = job.one - x0;                 // elements of the line from x0 on
+  const long long padded = job.dst_pitch - x0;          // destination elements from x0 on (a multiple of VEC)
+  const int count = static_cast<int>(valid < SEG ? valid : SEG);
+  const int out = static_cast<int>(padded < SEG ? padded : SEG);
+#pragma unroll 8
+  for (int i = threadIdx.x; i < out; i += 256) seg[i] = i < count ? src[i] : W(0);
+  __syncthreads();
+  uint4* __restrict__ dst = reinterpret_cast<uint4*>(static_cast<W*>(job.dst) + line * job.dst_pitch + x0);
+  const uint4* staged = reinterpret_cast<const uint4*>(seg);
+  for (int v = threadIdx.x; v < out / VEC; v += 256) dst[v] = staged[v];
 }
 
 }  // namespace
@@ -379,14 +430,18 @@ cudaError_t launch_invert_diagonal_blocks(int dtype, bool mem_upper, bool unit_d
 
 cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* im, long long im_off, void* col,
                           long long col_off, cudaStream_t stream, long long images, long long im_stride) {
-  const long long per_image = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w * out_h * g.out_w;
-  const long long total = per_image * images;
-  if (per_image <= 0 || images <= 0) return cudaErrorInvalidValue;
+  const long long rows = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w;
+  const long long plane = static_cast<long long>(out_h) * g.out_w;
+  if (rows <= 0 || plane <= 0 || images <= 0 || plane > 0x7FFFFFFF - kIm2colChunk) return cudaErrorInvalidValue;
+  const int chunks = static_cast<int>((plane + kIm2colChunk - 1) / kIm2colChunk);
+  const long long units = rows * chunks * images;
+  const long long cap = static_cast<long long>(sm_count() > 0 ? sm_count() : 1) * 64;
+  const unsigned grid = static_cast<unsigned>(units < cap ? units : cap);
   return by_dtype(dtype, [&](auto* tag) {
     using T = typename std::remove_pointer<decltype(tag)>::type;
-    im2col_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(g, out_h, per_image, total,
-                                                               static_cast<const T*>(im) + im_off, im_stride,
-                                                               static_cast<T*>(col) + col_off);
+    im2col_kernel<T><<<grid, 256, 0, stream>>>(g, out_h, static_cast<int>(plane), chunks, rows, images,
+                                               static_cast<const T*>(im) + im_off, im_stride,
+                                               static_cast<T*>(col) + col_off);
     return cudaGetLastError();
   });
 }
@@ -401,6 +456,28 @@ cudaError_t launch_col2im(int dtype, const ConvGeom& g, int out_h, const void* c
                                                                static_cast<T*>(im) + im_off);
     return cudaGetLastError();
   });
+}
+
+cudaError_t launch_repitch(int elem_bytes, const RepitchJob (&jobs)[2], cudaStream_t stream) {
+  if (elem_bytes != 2 && elem_bytes != 4) return cudaErrorInvalidValue;
+  const long long seg = kSegBytes / elem_bytes, vec = 16 / elem_bytes;
+  RepitchParams p = {};
+  long long blocks[2] = {0, 0};
+  for (int j = 0; j < 2; ++j) {
+    p.job[j] = jobs[j];
+    if (jobs[j].two <= 0 || jobs[j].one <= 0) { p.job[j].two = 0; p.segs_per_line[j] = 1; continue; }
+    if ((reinterpret_cast<uintptr_t>(jobs[j].dst) & 15) || (jobs[j].dst_pitch % vec) || jobs[j].dst_pitch < jobs[j].one)
+      return cudaErrorInvalidValue;
+    p.segs_per_line[j] = (jobs[j].dst_pitch + seg - 1) / seg;
+    blocks[j] = p.segs_per_line[j] * jobs[j].two;
+  }
+  p.first_block_of_second = blocks[0];
+  const long long total = blocks[0] + blocks[1];
+  if (total <= 0) return cudaSuccess;
+  if (total > 0x7FFFFFFFLL) return cudaErrorInvalidValue;
+  if (elem_bytes == 2) repitch_kernel<unsigned short><<<static_cast<unsigned>(total), 256, 0, stream>>>(p);
+  else repitch_kernel<unsigned int><<<static_cast<unsigned>(total), 256, 0, stream>>>(p);
+  return cudaGetLastError();
 }
 
 }  // namespace b200

@@ -39,4 +39,14 @@ cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* i
 cudaError_t launch_col2im(int dtype, const ConvGeom& g, int out_h, const void* col, long long col_off, void* im,
                           long long im_off, cudaStream_t stream);
 
+// Copies up to two matrices (`one` contiguous elements per line, `two` lines, any base alignment and leading dimension)
+// into destinations whose base is 16-byte aligned and whose pitch is a multiple of 16 bytes, in one launch; the padding
+// between `one` and the pitch is zero-filled. Element size 2 or 4 bytes. A job with two == 0 is skipped.
+struct RepitchJob {
+  const void* src;   // first element
+  void* dst;
+  long long one, two, src_ld, dst_pitch;  // elements
+};
+cudaError_t launch_repitch(int elem_bytes, const RepitchJob (&jobs)[2], cudaStream_t stream);
+
 }  // namespace b200

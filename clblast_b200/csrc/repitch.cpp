@@ -42,16 +42,17 @@ cudaError_t launch_repitched(const GemmDesc& d, cudaStream_t stream, const char*
   unsigned char* scratch = nullptr;
   cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&scratch), a_slot + b_bytes + 256, stream);
   if (err != cudaSuccess) return err;
-  const double one[2] = {1.0, 0.0};
   GemmDesc r = d;
+  RepitchJob jobs[2] = {};
   if (a_bad) {
-    err = launch_omatcopy(d.dtype, false, false, a_one, a_two, one, d.a, d.a_off, d.lda, scratch, 0, a_pitch, stream);
+    jobs[0] = {static_cast<const unsigned char*>(d.a) + d.a_off * elem, scratch, a_one, a_two, d.lda, a_pitch};
     r.a = scratch; r.a_off = 0; r.lda = a_pitch;
   }
-  if (err == cudaSuccess && b_bad) {
-    err = launch_omatcopy(d.dtype, false, false, b_one, b_two, one, d.b, d.b_off, d.ldb, scratch + a_slot, 0, b_pitch, stream);
+  if (b_bad) {
+    jobs[1] = {static_cast<const unsigned char*>(d.b) + d.b_off * elem, scratch + a_slot, b_one, b_two, d.ldb, b_pitch};
     r.b = scratch + a_slot; r.b_off = 0; r.ldb = b_pitch;
   }
+  err = launch_repitch(static_cast<int>(elem), jobs, stream);
   if (err == cudaSuccess) {
     const char* inner = "none";
     if (d.dtype == 16) {
