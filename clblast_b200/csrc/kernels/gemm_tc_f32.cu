@@ -88,9 +88,16 @@ template <int BN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
-  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // main (raw -> hi in place) and lo copies
-  static constexpr int STAGES = (BN == 256) ? 2 : (BN == 64) ? 4 : 3;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int MAIN_BYTES = A_BYTES + B_BYTES;  // one K block: raw fp32, turned into the big parts in place
+  // The big-part ring is held from the TMA issue until the MMAs have read it, so its depth is what hides the load
+  // latency; a small-part tile only lives from the split to the MMAs, so a shorter ring of its own is enough - but not
+  // much shorter: split -> MMA -> commit -> next split is a serial chain per slot (measured with 128x64 tiles: load
+  // ring 7 + 2 slots: 1024^3 35.6 us, 2048 x (64x128x96) 87 us; 6 + 3: 29.8 / 75.6 us; 4 + 4, the coupled ring this
+  // replaces: 30.0 / 64.7 us).
+  static constexpr int STAGES = (BN == 256) ? 2 : (BN == 64) ? 5 : 4;
+  static constexpr int LO_STAGES = (BN == 256) ? 2 : (BN == 64) ? 4 : 3;
+  static constexpr int SMEM_BYTES = (STAGES + LO_STAGES) * MAIN_BYTES + 1024 + 512;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
 };
 
 // Convolution tiles: m fastest, then n, then the image index.
@@ -122,6 +129,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const Tc32Params p) {
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES;
+  constexpr int LO_STAGES = C::LO_STAGES;
   constexpr bool CONV = MODE == kConv;
   constexpr bool GATHER = MODE == kGather;
   static_assert(!GATHER || BN == 128, "the gathered variant prefetches 16 + 16 values per thread");
@@ -129,15 +137,18 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
   uint8_t* const base_ptr = smem_raw + (tiles_base - raw);
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * C::STAGE_BYTES);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(base_ptr + (STAGES + LO_STAGES) * C::MAIN_BYTES);
   const uint32_t bar_base = smem_u32(bars);
-  // [0,S) raw data landed, [S,2S) split done, [2S,3S) stage free, then 2 partial-full, 2 partial-free
+  // [0,S) raw data landed, [S,2S) split done, [2S,3S) stage free, then 2 partial-full, 2 partial-free, L small-part
+  // slot free
   auto raw_full = [&](int s) { return bar_base + 8u * s; };
   auto split_full = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto stage_free = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
   auto part_full = [&](int a) { return bar_base + 8u * (3 * STAGES + a); };
   auto part_free = [&](int a) { return bar_base + 8u * (3 * STAGES + 2 + a); };
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
+  auto lo_free = [&](int l) { return bar_base + 8u * (3 * STAGES + 4 + l); };
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4 + LO_STAGES);
+  static_assert((3 * STAGES + 4 + LO_STAGES) * 8 + 8 <= 512, "barrier block");
   volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -165,6 +176,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(part_full(a), 1);
       mbar_init(part_free(a), 8);
     }
+    for (int l = 0; l < LO_STAGES; ++l) mbar_init(lo_free(l), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -174,11 +186,13 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // stage layout: A main | B main | A lo | B lo
-  auto a_main = [&](int s) { return tiles_base + s * C::STAGE_BYTES; };
+  // layout: STAGES x (A main | B main), then LO_STAGES x (A lo | B lo); K block g of this CTA uses main stage
+  // g % STAGES and small-part slot g % LO_STAGES
+  auto a_main = [&](int s) { return tiles_base + s * C::MAIN_BYTES; };
   auto b_main = [&](int s) { return a_main(s) + C::A_BYTES; };
-  auto a_lo = [&](int s) { return b_main(s) + C::B_BYTES; };
-  auto b_lo = [&](int s) { return a_lo(s) + C::A_BYTES; };
+  auto a_lo = [&](int l) { return tiles_base + (STAGES + l) * C::MAIN_BYTES; };
+  auto b_lo = [&](int l) { return a_lo(l) + C::A_BYTES; };
+  uint8_t* const lo_ring = base_ptr + STAGES * C::MAIN_BYTES;
 
   // Register budgets are re-balanced per warpgroup: producers need few, drain warps hold 128 accumulators each.
   if (warp < 4) {
@@ -188,6 +202,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int slot = 0;  // convolution: small-part slot the weights' small parts are loaded into
+      uint32_t slot_phase = 0;
       int issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -196,14 +212,18 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
+          if (CONV && !mbar_wait(lo_free(slot), slot_phase ^ 1u, abort_flag, 8u, p.status)) { ok = false; break; }
           if (GATHER) {
             mbar_arrive(raw_full(stage));  // nothing to load: tell the split warps the stage is theirs
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             continue;
           }
-          mbar_arrive_expect_tx(raw_full(stage), CONV ? C::B_BYTES : C::A_BYTES + C::B_BYTES);
+          mbar_arrive_expect_tx(raw_full(stage), CONV ? 2 * C::B_BYTES : C::A_BYTES + C::B_BYTES);
           if (CONV) {
-            // op(A) is gathered by the split warps
+            // op(A) is gathered by the split warps; the weights were split once for all tiles (map_b: big parts,
+            // map_a: small parts) and go straight to where the MMAs read them
+            tma_load_3d(b_lo(slot), &map_a, raw_full(stage), kb * BK, tn * BN, 0);
+            if (++slot == LO_STAGES) { slot = 0; slot_phase ^= 1u; }
           } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 32; ++j)
@@ -239,6 +259,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       constexpr uint32_t idesc = make_idesc(BM, BN, 2, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
+      int lo = 0;           // small-part slot of the current K block
       int chunk_index = 0;  // running count of partials produced by this CTA
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -251,6 +272,7 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
           for (int kb = kb0; kb < kb_end; ++kb) {
             if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, p.status)) { ok = false; break; }
+            if (CONV && !mbar_wait(raw_full(stage), phase, abort_flag, 9u, p.status)) { ok = false; break; }
             tcgen05_fence_after();
             // K-major: rows of 128 B along K (16-byte-chunk swizzle), advance 8 floats = 32 B per MMA.
             // MN-major: one 128-byte row per k (32-byte-chunk swizzle, atoms of four k = 512 B), eight k = 1024 B
@@ -263,15 +285,17 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int ks = 0; ks < BK / UMMA_K; ++ks) {
               const uint64_t a_hi = smem_desc(a_main(stage) + ks * a_step, a_lbo, a_sbo, a_type);
-              const uint64_t a_sm = smem_desc(a_lo(stage) + ks * a_step, a_lbo, a_sbo, a_type);
+              const uint64_t a_sm = smem_desc(a_lo(lo) + ks * a_step, a_lbo, a_sbo, a_type);
               const uint64_t b_hi = smem_desc(b_main(stage) + ks * b_step, b_lbo, b_sbo, b_type);
-              const uint64_t b_sm = smem_desc(b_lo(stage) + ks * b_step, b_lbo, b_sbo, b_type);
+              const uint64_t b_sm = smem_desc(b_lo(lo) + ks * b_step, b_lbo, b_sbo, b_type);
               umma_tf32(d_tmem, a_sm, b_hi, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);  // small terms first
               umma_tf32(d_tmem, a_hi, b_sm, idesc, 1u);
               umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
             }
             umma_commit(stage_free(stage));
+            umma_commit(lo_free(lo));
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++lo == LO_STAGES) lo = 0;
           }
           if (ok) umma_commit(part_full(part));  // this partial is complete
         }
@@ -390,11 +414,14 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if ((kbg & 1) != group) continue;
           const int st = kbg % STAGES;
           const uint32_t ph = static_cast<uint32_t>(kbg / STAGES) & 1u;
+          const int slot = kbg % LO_STAGES;
           ok = mbar_wait(raw_full(st), ph, abort_flag, 5u, p.status);
+          // the MMAs of K block kbg - LO_STAGES have read the slot (passes at once on its first use)
+          ok = ok && mbar_wait(lo_free(slot), (static_cast<uint32_t>(kbg / LO_STAGES) & 1u) ^ 1u, abort_flag, 7u, p.status);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + st * C::STAGE_BYTES);
-          float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + st * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+          float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + st * C::MAIN_BYTES);
+          float4* const lo_ptr = reinterpret_cast<float4*>(lo_ring + slot * C::MAIN_BYTES);
 #pragma unroll 4
           for (int c = gt; c < CHUNKS_ALL; c += 128) {
             const float4 x = main_ptr[c];
@@ -411,10 +438,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
     } else {
-    // GEMM: A and B main tiles are adjacent, so are the lo tiles, and all are split. Convolution: only B is split
-    // from its raw copy; A is produced below.
-    constexpr int CHUNKS = (C::A_BYTES + C::B_BYTES) / 16;
-    constexpr int CHUNK_FIRST = GATHER ? CHUNKS : CONV ? C::A_BYTES / 16 : 0;
+    // Nothing arrives raw in these variants: the split warps write the big and small parts of what they gather
+    // (convolution: of op(A) only; both parts of the weights come by TMA).
     // Convolution gather: this thread owns pixel group `pg` (8 consecutive output pixels = one 32-byte swizzle chunk)
     // of the 128-pixel tile and K rows `kr` and `kr + 16` of every K block.
     const int pg = t & 15, kr = t >> 4;
@@ -423,6 +448,8 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // load instruction reads one 128-byte run. Sixteen values per operand and K block are held in registers.
     const int sw = t >> 5;
     float ga[GATHER ? 16 : 1], gb[GATHER ? 16 : 1];
+    int slot = 0;           // small-part slot of the current K block
+    uint32_t slot_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tm = 0, tn = 0, image_index = 0;
       const float* image = nullptr;
@@ -564,11 +591,15 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         gather_plain(gb, b_src, p.ldb, B_MN, tn * BN, p.n, 0);
       }
       for (int kb = 0; kb < p.k_blocks; ++kb) {
-        ok = mbar_wait(raw_full(stage), phase, abort_flag, 5u, p.status);
+        // convolution: the stage is ours once its previous MMAs are done (the weights land in it independently and the
+        // MMA warp waits for them itself); gathered GEMM: the producer warp forwards "stage free" on raw_full
+        ok = CONV ? mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 5u, p.status)
+                  : mbar_wait(raw_full(stage), phase, abort_flag, 5u, p.status);
+        ok = ok && mbar_wait(lo_free(slot), slot_phase ^ 1u, abort_flag, 7u, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES);
-        float4* const lo_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES);
+        float4* const main_ptr = reinterpret_cast<float4*>(base_ptr + stage * C::MAIN_BYTES);
+        float4* const lo_ptr = reinterpret_cast<float4*>(lo_ring + slot * C::MAIN_BYTES);
         if constexpr (CONV) {
           // MN-major A tile with the 32-byte-chunk swizzle: column block pg/4 (4096 B each), row k (128 B), chunk
           // (pg % 4) ^ (k % 4) of 32 B holding this thread's eight pixels.
@@ -591,27 +622,20 @@ sgemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (kb + 1 < p.k_blocks) gather(kb + 1);  // in flight while B is split and the MMAs run
         }
         if constexpr (GATHER) {
-          uint8_t* const stage_ptr = base_ptr + stage * C::STAGE_BYTES;
-          store_plain(ga, stage_ptr, stage_ptr + C::A_BYTES + C::B_BYTES, A_MN);
-          store_plain(gb, stage_ptr + C::A_BYTES, stage_ptr + 2 * C::A_BYTES + C::B_BYTES, B_MN);
+          uint8_t* const stage_ptr = base_ptr + stage * C::MAIN_BYTES;
+          uint8_t* const slot_ptr = lo_ring + slot * C::MAIN_BYTES;
+          store_plain(ga, stage_ptr, slot_ptr, A_MN);
+          store_plain(gb, stage_ptr + C::A_BYTES, slot_ptr + C::A_BYTES, B_MN);
           if (kb + 1 < p.k_blocks) {  // in flight while the tensor cores work on this stage
             gather_plain(ga, a_src, p.lda, A_MN, tm * BM, p.m, kb + 1);
             gather_plain(gb, b_src, p.ldb, B_MN, tn * BN, p.n, kb + 1);
           }
         }
-#pragma unroll 4
-        for (int c = CHUNK_FIRST + t; c < CHUNKS; c += 256) {
-          const float4 x = main_ptr[c];
-          float4 hi, lo;
-          hi.x = to_tf32_big(x.x); hi.y = to_tf32_big(x.y); hi.z = to_tf32_big(x.z); hi.w = to_tf32_big(x.w);
-          lo.x = to_tf32(x.x - hi.x); lo.y = to_tf32(x.y - hi.y); lo.z = to_tf32(x.z - hi.z); lo.w = to_tf32(x.w - hi.w);
-          main_ptr[c] = hi;
-          lo_ptr[c] = lo;
-        }
         fence_proxy_async();  // the tensor cores read these tiles through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(split_full(stage));
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        if (++slot == LO_STAGES) { slot = 0; slot_phase ^= 1u; }
       }
     }
     }  // gathered / convolution variants
@@ -638,6 +662,24 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
   if (e != cudaSuccess) return e;
   kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma, mb, p);
   return cudaGetLastError();
+}
+
+#include "gemm_tc_f32_ts.cuh"
+
+// op(A) through tensor memory (gemm_tc_f32_ts.cuh) unless B200BLAS_SGEMM_TMEM_A=0 asks for the shared-memory kernels.
+bool tmem_a_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200BLAS_SGEMM_TMEM_A");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return on;
+}
+
+template <int BN>
+cudaError_t launch_ts(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid,
+                      cudaStream_t stream) {
+  if (a_mn) return b_mn ? ts::launch<BN, true, true>(ma, mb, p, grid, stream) : ts::launch<BN, true, false>(ma, mb, p, grid, stream);
+  return b_mn ? ts::launch<BN, false, true>(ma, mb, p, grid, stream) : ts::launch<BN, false, false>(ma, mb, p, grid, stream);
 }
 
 }  // namespace
@@ -731,6 +773,11 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
     return b_mn ? launch_variant<256, false, true>(map_a, map_b, p, grid, stream)
                 : launch_variant<256, false, false>(map_a, map_b, p, grid, stream);
   }
+  if (bn != 256 && tmem_a_enabled()) {
+    *name = bn == 64 ? "tc_f32_3xtf32_128x64x32_tmem_a" : "tc_f32_3xtf32_128x128x32_tmem_a";
+    return bn == 64 ? launch_ts<64>(a_mn, b_mn, map_a, map_b, p, grid, stream)
+                    : launch_ts<128>(a_mn, b_mn, map_a, map_b, p, grid, stream);
+  }
   if (bn == 64) {
     *name = "tc_f32_3xtf32_128x64x32";
     if (a_mn) {
@@ -805,8 +852,12 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
   int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  *name = "tc_f32_3xtf32_narrow_128x64x32";
   const bool a_mn = !d.b_kcontig, b_mn = !d.a_kcontig;
+  if (tmem_a_enabled()) {
+    *name = "tc_f32_3xtf32_narrow_128x64x32_tmem_a";
+    return launch_ts<BN>(a_mn, b_mn, map_a, map_b, p, grid, stream);
+  }
+  *name = "tc_f32_3xtf32_narrow_128x64x32";
   if (a_mn) {
     return b_mn ? launch_variant<BN, true, true>(map_a, map_b, p, grid, stream)
                 : launch_variant<BN, true, false>(map_a, map_b, p, grid, stream);
@@ -815,6 +866,22 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
               : launch_variant<BN, false, false>(map_a, map_b, p, grid, stream);
 }
 
+namespace {
+// Big and small TF32 parts of the weights [rows][k] (leading dimension ld) into two planes with pitch `pitch`.
+__global__ void split_weights_kernel(const float* __restrict__ w, long long ld, int rows, int k, int pitch,
+                                     float* __restrict__ big, float* __restrict__ small) {
+  const long long total = static_cast<long long>(rows) * pitch;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / pitch), c = static_cast<int>(i - static_cast<long long>(r) * pitch);
+    const float x = c < k ? w[r * ld + c] : 0.f;
+    const float hi = tc::to_tf32_big(x);
+    big[i] = hi;
+    small[i] = tc::to_tf32(x - hi);
+  }
+}
+}  // namespace
+
 cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if (d.dtype != 32 || !d.is_conv) return cudaErrorNotSupported;
   static const bool forced_ffma = [] {
@@ -822,16 +889,36 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
     return v != nullptr && std::strcmp(v, "ffma") == 0;
   }();
   if (forced_ffma) return cudaErrorNotSupported;
-  // weights [Cout][K] are the K-major B operand of the TMA path: 16-byte aligned rows
   const float* weights = static_cast<const float*>(d.b) + d.b_off;
-  if ((reinterpret_cast<uintptr_t>(weights) & 15) || (d.ldb % 4)) return cudaErrorNotSupported;
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF || d.batch > 0x7FFFFFFF) return cudaErrorNotSupported;
   constexpr int BN = 128;
   const long long tiles = ((d.m + BM - 1) / BM) * ((d.n + BN - 1) / BN) * d.batch;
   if (d.m < 128 || d.n < 32 || d.k < 64 || tiles < 64 || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
 
-  CUtensorMap map_b;
-  if (!encode_operand_map(&map_b, 4, weights, d.n, d.k, d.ldb, false, BN, 1, 0)) return cudaErrorNotSupported;
+  // The weights [Cout][K] are the K-major B operand of every tile of every image: they are split once into two planes
+  // of stream-ordered scratch (pitch rounded up to 16 bytes, so any K and any alignment of the caller's buffer will
+  // do), and both planes travel by TMA.
+  const long long pitch = (d.k + 3) / 4 * 4;
+  const size_t plane_bytes = (static_cast<size_t>(d.n) * pitch * 4 + 255) / 256 * 256;
+  float* planes = nullptr;
+  cudaError_t err = cudaMallocAsync(reinterpret_cast<void**>(&planes), 2 * plane_bytes, stream);
+  if (err != cudaSuccess) return err;
+  float* const small_plane = planes + plane_bytes / 4;
+  struct Release {  // stream-ordered: the kernels enqueued below still see the planes
+    float* ptr; cudaStream_t stream;
+    ~Release() { cudaFreeAsync(ptr, stream); }
+  } release{planes, stream};
+  CUtensorMap map_b, map_small;
+  if (!encode_operand_map(&map_b, 4, planes, d.n, d.k, pitch, false, BN, 1, 0)) return cudaErrorNotSupported;
+  if (!encode_operand_map(&map_small, 4, small_plane, d.n, d.k, pitch, false, BN, 1, 0)) return cudaErrorNotSupported;
+  {
+    const long long total = d.n * pitch;
+    const unsigned blocks = static_cast<unsigned>(total / 256 + 1 < 4096 ? total / 256 + 1 : 4096);
+    split_weights_kernel<<<blocks, 256, 0, stream>>>(weights, d.ldb, static_cast<int>(d.n), static_cast<int>(d.k),
+                                                     static_cast<int>(pitch), planes, small_plane);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+  }
 
   Tc32Params p = {};
   p.status = tc_status_device();
@@ -871,8 +958,19 @@ cudaError_t launch_tc_conv_f32(const GemmDesc& d, cudaStream_t stream, const cha
   int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  // The tensor-memory kernel addresses the image with 32-bit offsets and keeps a table of the K rows in shared memory.
+  const long long image_span = (static_cast<long long>(d.conv.channels) * d.conv.height +
+                                static_cast<long long>(d.conv.kernel_h) * d.conv.dil_h + d.conv.pad_h + d.conv.stride_h) *
+                                   d.conv.width + static_cast<long long>(d.conv.kernel_w) * d.conv.dil_w;
+  const bool taps_fit = d.conv.height < 0x7000 && d.conv.width < 0x7000 && d.conv.pad_h < 0x800 &&
+                        static_cast<long long>(d.conv.kernel_h) * d.conv.dil_h < 0x7000 &&
+                        static_cast<long long>(d.conv.kernel_w) * d.conv.dil_w < 0x7000;
+  if (tmem_a_enabled() && taps_fit && image_span < 0x20000000LL && ts::smem_bytes<BN, true>(p) <= 227 * 1024) {
+    *name = "tc_conv_f32_3xtf32_128x128x32_tmem_a";
+    return ts::launch<BN, false, false, true>(map_small, map_b, p, grid, stream);
+  }
   *name = "tc_conv_f32_3xtf32_128x128x32";
-  return launch_variant<BN, true, false, kConv>(map_b, map_b, p, grid, stream);
+  return launch_variant<BN, true, false, kConv>(map_small, map_b, p, grid, stream);
 }
 
 }  // namespace b200

@@ -247,41 +247,39 @@ __global__ void __launch_bounds__(NB) invert_blocks_kernel(long long k, const T*
 
 // ---- im2col / col2im ----------------------------------------------------------------------------------------------------
 
-// One CTA writes kIm2colChunk consecutive elements of one row (channel, kernel index) of one image's column matrix:
-// the row's tap is decoded once per CTA, and each thread walks its output pixels with additions only.
-constexpr int kIm2colChunk = 2048;
+// One CTA writes one row (channel, kernel index) of one image's column matrix, or several whole rows when a row is
+// shorter than the CTA: the row's tap is decoded once per thread, and each thread walks its output pixels with
+// additions only. blockIdx.x: row group, blockIdx.y: image (strided when there are more images than grid rows).
 template <typename T>
-__global__ void __launch_bounds__(256) im2col_kernel(ConvGeom g, int out_h, int plane, int chunks, long long rows,
+__global__ void __launch_bounds__(256) im2col_kernel(ConvGeom g, int out_h, int plane, int rows_per_cta, int rows,
                                                      long long images, const T* __restrict__ im_all,
                                                      long long im_stride, T* __restrict__ col) {
   const int khw = g.kernel_h * g.kernel_w;
-  const long long units = rows * chunks;  // per image
-  const int step_h = 256 / g.out_w, step_w = 256 - step_h * g.out_w;
-  for (long long unit = blockIdx.x; unit < units * images; unit += gridDim.x) {
-    const long long image_index = unit / units;
-    const long long in_image = unit - image_index * units;
-    const long long row = in_image / chunks;
-    const int chunk = static_cast<int>(in_image - row * chunks);
-    const int c = static_cast<int>(row / khw);
-    const int kidx = static_cast<int>(row - static_cast<long long>(c) * khw);
-    const int tap = g.flip ? khw - 1 - kidx : kidx;  // the tap whose value lands at this kernel index
-    const int kh = tap / g.kernel_w, kw = tap - kh * g.kernel_w;
-    const int dh = kh * g.dil_h - g.pad_h, dw = kw * g.dil_w - g.pad_w;
+  const int tid = static_cast<int>(threadIdx.x);
+  const int local = rows_per_cta > 1 ? tid / plane : 0;
+  const int first = rows_per_cta > 1 ? tid - local * plane : tid;
+  const int step = rows_per_cta > 1 ? plane : 256;  // several rows per CTA: one element per thread
+  const int row = static_cast<int>(blockIdx.x) * rows_per_cta + local;
+  if (local >= rows_per_cta || row >= rows) return;
+  const int c = row / khw;
+  const int kidx = row - c * khw;
+  const int tap = g.flip ? khw - 1 - kidx : kidx;  // the tap whose value lands at this kernel index
+  const int kh = tap / g.kernel_w, kw = tap - kh * g.kernel_w;
+  const int dh = kh * g.dil_h - g.pad_h, dw = kw * g.dil_w - g.pad_w;
+  const int step_h = step / g.out_w, step_w = step - step_h * g.out_w;
+  const int ho0 = first / g.out_w, wo0 = first - ho0 * g.out_w;
+  for (long long image_index = blockIdx.y; image_index < images; image_index += gridDim.y) {
     const T* __restrict__ im = im_all + image_index * im_stride + static_cast<long long>(c) * g.height * g.width;
     T* __restrict__ out = col + (image_index * rows + row) * plane;  // column matrices of consecutive images are adjacent
-    int pos = chunk * kIm2colChunk + threadIdx.x;
-    int ho = pos / g.out_w, wo = pos - ho * g.out_w;
+    int ho = ho0, wo = wo0;
 #pragma unroll 4
-    for (int i = 0; i < kIm2colChunk / 256; ++i) {
-      if (pos < plane) {
-        const int h = ho * g.stride_h + dh, w = wo * g.stride_w + dw;
-        T v = El<T>::zero();
-        if (static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
-            static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
-          v = im[static_cast<long long>(h) * g.width + w];
-        out[pos] = v;
-      }
-      pos += 256;
+    for (int pos = first; pos < plane; pos += step) {
+      const int h = ho * g.stride_h + dh, w = wo * g.stride_w + dw;
+      T v = El<T>::zero();
+      if (static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
+          static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
+        v = im[static_cast<long long>(h) * g.width + w];
+      out[pos] = v;
       ho += step_h;
       wo += step_w;
       if (wo >= g.out_w) { wo -= g.out_w; ++ho; }
@@ -331,8 +329,9 @@ unsigned grid_for(long long total, int threads) {
 
 // ---- re-pitching copy -------------------------------------------------------------------------------------------------
 
-// One CTA moves one segment of kSegBytes of one line: coalesced element loads from the (arbitrarily aligned) source
-// into shared memory, then 16-byte stores to the aligned destination. Both jobs share the launch.
+// Every thread produces two 16-byte vectors of the aligned destination from element loads of the (arbitrarily aligned)
+// source: the loads of a warp cover one contiguous run, so every sector is fetched from L2 once, and nothing waits on
+// anything else. One CTA covers kSegBytes of one line; both jobs share the launch.
 constexpr int kSegBytes = 8192;
 struct RepitchParams {
   RepitchJob job[2];
@@ -344,7 +343,6 @@ template <typename W>  // W: an unsigned type of the element's width
 __global__ void __launch_bounds__(256) repitch_kernel(const RepitchParams p) {
   constexpr int SEG = kSegBytes / static_cast<int>(sizeof(W));
   constexpr int VEC = 16 / static_cast<int>(sizeof(W));
-  __shared__ __align__(16) W seg[SEG];
   long long block = blockIdx.x;
   const int which = block >= p.first_block_of_second ? 1 : 0;
   if (which) block -= p.first_block_of_second;
@@ -352,16 +350,23 @@ __global__ void __launch_bounds__(256) repitch_kernel(const RepitchParams p) {
   const long long line = block / p.segs_per_line[which];
   const long long x0 = (block - line * p.segs_per_line[which]) * SEG;
   const W* __restrict__ src = static_cast<const W*>(job.src) + line * job.src_ld + x0;
-  const long long valid = job.one - x0;                 // elements of the line from x0 on
-  const long long padded = job.dst_pitch - x0;          // destination elements from x0 on (a multiple of VEC)
-  const int count = static_cast<int>(valid < SEG ? valid : SEG);
-  const int out = static_cast<int>(padded < SEG ? padded : SEG);
-#pragma unroll 8
-  for (int i = threadIdx.x; i < out; i += 256) seg[i] = i < count ? src[i] : W(0);
-  __syncthreads();
-  uint4* __restrict__ dst = reinterpret_cast<uint4*>(static_cast<W*>(job.dst) + line * job.dst_pitch + x0);
-  const uint4* staged = reinterpret_cast<const uint4*>(seg);
-  for (int v = threadIdx.x; v < out / VEC; v += 256) dst[v] = staged[v];
+  W* __restrict__ dst = static_cast<W*>(job.dst) + line * job.dst_pitch + x0;
+  const long long valid_ll = job.one - x0, padded_ll = job.dst_pitch - x0;  // source / destination elements from x0 on
+  const int valid = static_cast<int>(valid_ll < SEG ? valid_ll : SEG);
+  const int padded = static_cast<int>(padded_ll < SEG ? padded_ll : SEG);   // a multiple of VEC
+  union Vec { uint4 v; W e[VEC]; };
+  Vec r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int i0 = (static_cast<int>(threadIdx.x) + 256 * h) * VEC;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) r[h].e[j] = (i0 + j < valid) ? src[i0 + j] : W(0);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int i0 = (static_cast<int>(threadIdx.x) + 256 * h) * VEC;
+    if (i0 < padded) *reinterpret_cast<uint4*>(dst + i0) = r[h].v;
+  }
 }
 
 }  // namespace
@@ -432,15 +437,17 @@ cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* i
                           long long col_off, cudaStream_t stream, long long images, long long im_stride) {
   const long long rows = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w;
   const long long plane = static_cast<long long>(out_h) * g.out_w;
-  if (rows <= 0 || plane <= 0 || images <= 0 || plane > 0x7FFFFFFF - kIm2colChunk) return cudaErrorInvalidValue;
-  const int chunks = static_cast<int>((plane + kIm2colChunk - 1) / kIm2colChunk);
-  const long long units = rows * chunks * images;
-  const long long cap = static_cast<long long>(sm_count() > 0 ? sm_count() : 1) * 64;
-  const unsigned grid = static_cast<unsigned>(units < cap ? units : cap);
+  if (rows <= 0 || plane <= 0 || images <= 0 || plane > 0x7FFFFFFF - 256 || rows > 0x7FFFFFFF - 256)
+    return cudaErrorInvalidValue;
+  const int rows_per_cta = plane >= 256 ? 1 : static_cast<int>(256 / plane);
+  const unsigned groups = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
+  // every thread decodes its tap and first pixel once (five integer divisions) and then walks eight images or more
+  const long long image_groups = (images + 7) / 8;
+  const dim3 grid(groups, static_cast<unsigned>(image_groups < 65535 ? image_groups : 65535));
   return by_dtype(dtype, [&](auto* tag) {
     using T = typename std::remove_pointer<decltype(tag)>::type;
-    im2col_kernel<T><<<grid, 256, 0, stream>>>(g, out_h, static_cast<int>(plane), chunks, rows, images,
-                                               static_cast<const T*>(im) + im_off, im_stride,
+    im2col_kernel<T><<<grid, 256, 0, stream>>>(g, out_h, static_cast<int>(plane), rows_per_cta, static_cast<int>(rows),
+                                               images, static_cast<const T*>(im) + im_off, im_stride,
                                                static_cast<T*>(col) + col_off);
     return cudaGetLastError();
   });

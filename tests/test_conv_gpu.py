@@ -66,8 +66,9 @@ def test_tensor_core_convolution_path(cuda, mode):
         (16, 40, 37, 3, 3, 1, 2, 1, 96, 24),     # stride 2, ragged width, Cout below one tile
         (12, 33, 35, 5, 3, 2, 1, 2, 200, 6),     # rectangular kernel, dilation 2, K = 180 (tail), Cout over one tile
         (64, 28, 28, 1, 1, 0, 1, 1, 64, 16),     # pointwise
-        (48, 70, 7, 3, 3, 1, 1, 1, 64, 8),       # rows of 7 output pixels: the gather with per-pixel divisions
-        (24, 50, 11, 3, 3, 1, 1, 1, 64, 8),      # rows of 11: groups of eight pixels straddle two rows in every phase
+        (48, 70, 7, 3, 3, 1, 1, 1, 64, 16),      # rows of 7 output pixels: the gather with per-pixel divisions
+        (24, 50, 11, 3, 3, 1, 1, 1, 64, 16),     # rows of 11: groups of eight pixels straddle two rows in every phase
+        (9, 64, 64, 3, 3, 1, 1, 1, 64, 4),       # K = 81: weight rows that are not a multiple of 16 bytes
     ]
     for ch, h, w, kh, kw, pad, stride, dil, nk, batch in cases:
         oh, ow = oracle.conv_output_size(h, w, kh, kw, pad, pad, stride, stride, dil, dil)
