@@ -242,3 +242,58 @@ def test_large_problems_with_unaligned_operands_are_repitched(cuda, precision):
         got = c.cpu().numpy().astype(np.float64)[cols * ldc + rows]
         assert (np.abs(got - want) / mag).max() < (2.0 ** -20 if precision == 32 else 2e-3)
         assert torch.equal(c.view(n, ldc)[:, m:], c0.view(n, ldc)[:, m:])
+
+
+_VARIANT_SCRIPT = r"""
+import hashlib, sys
+import torch
+import clblast_b200 as cb
+ROW, COL, NO, YES = 101, 102, 111, 112
+g = torch.Generator(device="cuda").manual_seed(5)
+def rnd(n):
+    return torch.rand(n, generator=g, device="cuda") * 2 - 1
+out = []
+# 128 x 64 tiles (few tiles), 128 x 128 tiles, a narrow batch, a convolution
+for (layout, ta, tb, m, n, k) in ((ROW, NO, NO, 1024, 1024, 1024), (COL, YES, NO, 1536, 1280, 520), (COL, NO, YES, 768, 520, 392)):
+    a, b, c = rnd(m * k), rnd(k * n), rnd(m * n)
+    lda = (k if ta == NO else m) if layout == ROW else (m if ta == NO else k)
+    ldb = (n if tb == NO else k) if layout == ROW else (k if tb == NO else n)
+    ldc = n if layout == ROW else m
+    assert cb.Gemm(layout, ta, tb, m, n, k, 0.7, a, 0, lda, b, 0, ldb, 0.3, c, 0, ldc) == 0
+    out.append((cb.last_kernel(), c))
+m, n, k, batch = 48, 200, 72, 400
+a, b, c = rnd(batch * m * k), rnd(batch * k * n), rnd(batch * m * n)
+assert cb.GemmStridedBatched(COL, NO, NO, m, n, k, 1.0, a, 0, m, m * k, b, 0, k, k * n, 1.0, c, 0, m, m * n, batch) == 0
+out.append((cb.last_kernel(), c))
+im, ker = rnd(8 * 32 * 40 * 37), rnd(96 * 32 * 9)
+res = torch.zeros(8 * 96 * 40 * 37, device="cuda")
+assert cb.Convgemm(151, 32, 40, 37, 3, 3, 1, 1, 1, 1, 1, 1, 96, 8, im, 0, ker, 0, res, 0) == 0
+out.append((cb.last_kernel(), res))
+torch.cuda.synchronize()
+for name, t in out:
+    print(name, hashlib.sha256(t.cpu().numpy().tobytes()).hexdigest())
+"""
+
+
+def test_tensor_memory_and_shared_memory_variants_agree_bit_for_bit(cuda):
+    """The kernels that keep op(A) in tensor memory and the ones that keep it in shared memory (B200BLAS_SGEMM_TMEM_A=0)
+    run the same MMAs in the same order on the same TF32 parts: identical bits on 128 x 64 and 128 x 128 tiles, a
+    narrow batch and a convolution. Each variant runs in a process of its own (the switch is read once)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    runs = {}
+    for switch in ("1", "0"):
+        env = dict(os.environ, B200BLAS_SGEMM_TMEM_A=switch, PYTHONPATH=str(root))
+        res = subprocess.run([sys.executable, "-c", _VARIANT_SCRIPT], capture_output=True, text=True, env=env, cwd=root,
+                             timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        runs[switch] = [line.split() for line in res.stdout.strip().splitlines()]
+    assert len(runs["1"]) == len(runs["0"]) == 5
+    for (name_tm, digest_tm), (name_sm, digest_sm) in zip(runs["1"], runs["0"]):
+        assert name_tm.endswith("_tmem_a") and name_tm.startswith(("tc_f32", "tc_conv")), name_tm
+        assert not name_sm.endswith("_tmem_a") and name_sm.startswith(("tc_f32", "tc_conv")), name_sm
+        assert digest_tm == digest_sm, (name_tm, name_sm)
