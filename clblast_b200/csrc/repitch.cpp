@@ -11,6 +11,8 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
 #include "kernels/launchers.h"
 #include "kernels/level3_aux.h"
@@ -20,6 +22,11 @@ namespace b200 {
 cudaError_t launch_repitched(const GemmDesc& d, cudaStream_t stream, const char** name) {
   if ((d.dtype != 16 && d.dtype != 32) || d.is_conv || d.force_small || d.batch != 1 || d.a_offs || d.conj_a || d.conj_b)
     return cudaErrorNotSupported;
+  static const bool disabled = [] {  // B200BLAS_REPITCH=0: keep the in-kernel gather / the CUDA-core kernel
+    const char* v = std::getenv("B200BLAS_REPITCH");
+    return v != nullptr && std::strcmp(v, "0") == 0;
+  }();
+  if (disabled) return cudaErrorNotSupported;
   const long long elem = d.dtype == 16 ? 2 : 4, gran = 16 / elem;
   const auto misaligned = [&](const void* base, long long off, long long ld) {
     return ((reinterpret_cast<uintptr_t>(base) + static_cast<uintptr_t>(off * elem)) & 15) != 0 || (ld % gran) != 0;
