@@ -266,23 +266,28 @@ __global__ void __launch_bounds__(256) im2col_kernel(ConvGeom g, int out_h, int 
   const int tap = g.flip ? khw - 1 - kidx : kidx;  // the tap whose value lands at this kernel index
   const int kh = tap / g.kernel_w, kw = tap - kh * g.kernel_w;
   const int dh = kh * g.dil_h - g.pad_h, dw = kw * g.dil_w - g.pad_w;
+  // A thread's pixels are `step` apart: step_h rows and step_w columns further, one more row on a wrap. Row, column and
+  // offset inside the channel plane of the tap it reads move by constants, so the loop body is additions and compares.
   const int step_h = step / g.out_w, step_w = step - step_h * g.out_w;
   const int ho0 = first / g.out_w, wo0 = first - ho0 * g.out_w;
+  const int h_step = step_h * g.stride_h, w_step = step_w * g.stride_w;
+  const int off_step = h_step * g.width + w_step;
+  const int w_wrap = g.out_w * g.stride_w, off_wrap = g.stride_h * g.width - w_wrap;
   for (long long image_index = blockIdx.y; image_index < images; image_index += gridDim.y) {
     const T* __restrict__ im = im_all + image_index * im_stride + static_cast<long long>(c) * g.height * g.width;
     T* __restrict__ out = col + (image_index * rows + row) * plane;  // column matrices of consecutive images are adjacent
-    int ho = ho0, wo = wo0;
+    int wo = wo0;
+    int h = ho0 * g.stride_h + dh, w = wo0 * g.stride_w + dw;
+    int off = h * g.width + w;
 #pragma unroll 4
     for (int pos = first; pos < plane; pos += step) {
-      const int h = ho * g.stride_h + dh, w = wo * g.stride_w + dw;
       T v = El<T>::zero();
       if (static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
           static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
-        v = im[static_cast<long long>(h) * g.width + w];
+        v = im[off];
       out[pos] = v;
-      ho += step_h;
-      wo += step_w;
-      if (wo >= g.out_w) { wo -= g.out_w; ++ho; }
+      h += h_step; w += w_step; off += off_step; wo += step_w;
+      if (wo >= g.out_w) { wo -= g.out_w; w -= w_wrap; h += g.stride_h; off += off_wrap; }
     }
   }
 }
@@ -437,7 +442,12 @@ cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* i
                           long long col_off, cudaStream_t stream, long long images, long long im_stride) {
   const long long rows = static_cast<long long>(g.channels) * g.kernel_h * g.kernel_w;
   const long long plane = static_cast<long long>(out_h) * g.out_w;
-  if (rows <= 0 || plane <= 0 || images <= 0 || plane > 0x7FFFFFFF - 256 || rows > 0x7FFFFFFF - 256)
+  // offsets inside one channel plane, padding and the last partial step included, are kept in 32 bits
+  const long long reach = (static_cast<long long>(g.height) + 2LL * (g.pad_h > 0 ? g.pad_h : 0) +
+                           static_cast<long long>(g.kernel_h) * g.dil_h + 512LL * g.stride_h) * g.width +
+                          static_cast<long long>(g.kernel_w) * g.dil_w + 512LL * g.stride_w + g.pad_w;
+  if (rows <= 0 || plane <= 0 || images <= 0 || plane > 0x7FFFFFFF - 256 || rows > 0x7FFFFFFF - 256 ||
+      reach > 0x7FFFFFFF)
     return cudaErrorInvalidValue;
   const int rows_per_cta = plane >= 256 ? 1 : static_cast<int>(256 / plane);
   const unsigned groups = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
