@@ -715,7 +715,16 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   // Small problems: when twice as many tiles still fit the machine in one wave, 64-column tiles put twice as many
   // SMs to work (1024^3: 64 -> 128 CTAs, 56 -> 66 TFLOP/s).
   const long long tiles_128 = ((d.m + BM - 1) / BM) * ((d.n + 127) / 128) * walk.batches;
-  if (!gathered && bn == 128 && 2 * tiles_128 <= device_sms) bn = 64;
+  // Better still, with op(A) in tensor memory: keep 128 columns and let the two CTAs of a cluster take half of K each.
+  bool split_k = false;
+  if (!gathered && bn == 128 && 2 * tiles_128 <= device_sms) {
+    static const bool no_split = [] {
+      const char* v = std::getenv("B200BLAS_SGEMM_SPLITK");
+      return v != nullptr && std::strcmp(v, "0") == 0;
+    }();
+    split_k = tmem_a_enabled() && !no_split && d.k >= 8 * BK && sm_budget() <= 0;
+    if (!split_k) bn = 64;
+  }
 
   CUtensorMap map_a, map_b;
   if (gathered) {
@@ -772,6 +781,16 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
     }
     return b_mn ? launch_variant<256, false, true>(map_a, map_b, p, grid, stream)
                 : launch_variant<256, false, false>(map_a, map_b, p, grid, stream);
+  }
+  if (split_k) {
+    *name = "tc_f32_3xtf32_128x128x32_splitk2_tmem_a";
+    const int t = static_cast<int>(tiles);
+    if (a_mn) {
+      return b_mn ? ts::launch_splitk<128, true, true>(map_a, map_b, p, t, stream)
+                  : ts::launch_splitk<128, true, false>(map_a, map_b, p, t, stream);
+    }
+    return b_mn ? ts::launch_splitk<128, false, true>(map_a, map_b, p, t, stream)
+                : ts::launch_splitk<128, false, false>(map_a, map_b, p, t, stream);
   }
   if (bn != 256 && tmem_a_enabled()) {
     *name = bn == 64 ? "tc_f32_3xtf32_128x64x32_tmem_a" : "tc_f32_3xtf32_128x128x32_tmem_a";

@@ -68,7 +68,17 @@ __device__ __forceinline__ void split_store_8(uint32_t big_col, const float (&x)
   tmem_st_8cols(big_col + 32u, lo);
 }
 
-template <int BN, bool A_MN, bool B_MN, bool CONV>
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+// SPLITK: launched as clusters of two CTAs with exactly one tile per cluster; CTA r of the cluster multiplies the r-th
+// half of K, CTA 1 hands its sums to CTA 0 through distributed shared memory, CTA 0 adds them and writes C. For
+// problems with so few tiles that half the SMs would idle (1024^3: 64 tiles of 128 x 128 on 128 SMs, each with half
+// as many K blocks as a 128 x 64 tile would need, and MMAs twice as wide for little more issue time).
+template <int BN, bool A_MN, bool B_MN, bool CONV, bool SPLITK = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const Tc32Params p) {
@@ -103,6 +113,14 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     z = tile / tiles_per_problem;
     tile_coords(p, tile - z * tiles_per_problem, tm, tn);
   };
+  static_assert(!(SPLITK && CONV), "the convolution is not split along K");
+  const int crank = SPLITK ? static_cast<int>(cluster_ctarank()) : 0;
+  const int first_tile = SPLITK ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = SPLITK ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  // this CTA's share of the K blocks
+  const int kb_half = (p.k_blocks + 1) / 2;
+  const int kb_begin = SPLITK ? crank * kb_half : 0;
+  const int kb_count = SPLITK ? min(kb_half, p.k_blocks - kb_begin) : p.k_blocks;
   constexpr int SPLIT_REGS = CONV ? 112 : 72;  // the convolution keeps 32 gathered values in flight
   constexpr int DRAIN_REGS = CONV ? 104 : 136;
   static_assert(BN <= 128, "the drain warps hold BN / 2 accumulators in 136 registers");
@@ -166,11 +184,11 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int stage = 0, slot = 0, issued = 0;
         uint32_t phase = 0, slot_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
           int tm, tn, image_index = 0, z = 0;
           if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else gemm_tile(tile, tm, tn, z);
           const int az = p.a_batched ? z : 0, bz = p.b_batched ? z : 0;
-          for (int kb = 0; kb < p.k_blocks; ++kb) {
+          for (int kb = 0; kb < kb_count; ++kb) {
             if (!mbar_wait(stage_free(stage), phase ^ 1u, abort_flag, 1u, p.status)) { ok = false; break; }
             if (CONV) {
               // both parts of the weights were prepared once for all tiles: map_b the big parts, map_a the small ones
@@ -184,16 +202,16 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               if (A_MN) {
 #pragma unroll
                 for (int j = 0; j < BM / 32; ++j)
-                  tma_load_3d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, kb * BK, az);
+                  tma_load_3d(a_main(stage) + j * 4096, &map_a, raw_full(stage), tm * BM + j * 32, (kb_begin + kb) * BK, az);
               } else {
-                tma_load_3d(a_main(stage), &map_a, raw_full(stage), kb * BK, tm * BM, az);
+                tma_load_3d(a_main(stage), &map_a, raw_full(stage), (kb_begin + kb) * BK, tm * BM, az);
               }
               if (B_MN) {
 #pragma unroll
                 for (int j = 0; j < BN / 32; ++j)
-                  tma_load_3d(b_main(stage) + j * 4096, &map_b, raw_full(stage), tn * BN + j * 32, kb * BK, bz);
+                  tma_load_3d(b_main(stage) + j * 4096, &map_b, raw_full(stage), tn * BN + j * 32, (kb_begin + kb) * BK, bz);
               } else {
-                tma_load_3d(b_main(stage), &map_b, raw_full(stage), kb * BK, tn * BN, bz);
+                tma_load_3d(b_main(stage), &map_b, raw_full(stage), (kb_begin + kb) * BK, tn * BN, bz);
               }
             }
             ++issued;
@@ -218,14 +236,14 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int stage = 0, lo = 0, chunk_index = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-          for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += CHUNK_KB, ++chunk_index) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+          for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, ++chunk_index) {
             const int part = chunk_index & 1;
             const uint32_t part_phase = (chunk_index >> 1) & 1u;
             if (!mbar_wait(part_free(part), part_phase ^ 1u, abort_flag, 2u, p.status)) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(part * BN);
-            const int kb_end = min(kb0 + CHUNK_KB, p.k_blocks);
+            const int kb_end = min(kb0 + CHUNK_KB, kb_count);
             for (int kb = kb0; kb < kb_end; ++kb) {
               if (!mbar_wait(split_full(stage), phase, abort_flag, 3u, p.status)) { ok = false; break; }
               if (CONV && !mbar_wait(raw_full(stage), phase, abort_flag, 9u, p.status)) { ok = false; break; }
@@ -258,8 +276,9 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int quad = warp & 3;
     const int half = (warp - 12) >> 2;
     int chunk_index = 0;
+    int cluster_syncs = 0;  // SPLITK: every thread of the cluster passes the cluster barrier exactly twice
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       int tm, tn, image_index = 0, z = 0;
       if (CONV) conv_tile_coords(p, tile, tm, tn, image_index); else gemm_tile(tile, tm, tn, z);
       const float alpha = (!CONV && p.alphas) ? p.alphas[z] : p.alpha;
@@ -268,7 +287,7 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       float acc[BN / 2];
 #pragma unroll
       for (int j = 0; j < BN / 2; ++j) acc[j] = 0.f;
-      for (int kb0 = 0; kb0 < p.k_blocks; kb0 += CHUNK_KB, ++chunk_index) {
+      for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, ++chunk_index) {
         const int part = chunk_index & 1;
         const uint32_t part_phase = (chunk_index >> 1) & 1u;
         ok = mbar_wait(part_full(part), part_phase, abort_flag, 4u, p.status);
@@ -289,6 +308,25 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (lane == 0) mbar_arrive(part_free(part));
       }
       if (!ok) break;
+      if constexpr (SPLITK) {
+        // The rings are idle now (every load has landed, every MMA has read its operands): CTA 1 leaves its sums in
+        // its own shared memory, [column][thread] so that neither side has bank conflicts, and CTA 0 fetches them.
+        float* const scratch = reinterpret_cast<float*>(base_ptr);
+        const int dt = static_cast<int>(threadIdx.x) - 12 * 32;
+        if (crank == 1) {
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j) scratch[j * 256 + dt] = acc[j];
+        }
+        cluster_sync_all();
+        if (crank == 0) {
+          const uint32_t peer = map_to_cta(smem_u32(scratch), 1u);
+#pragma unroll
+          for (int j = 0; j < BN / 2; ++j) acc[j] += ld_cluster_f32(peer + static_cast<uint32_t>(j * 256 + dt) * 4u);
+        }
+        cluster_sync_all();  // CTA 1 stays until its memory has been read
+        cluster_syncs = 2;
+        if (crank != 0) continue;
+      }
       const int row = tm * BM + quad * 32 + lane;
       const int col0 = tn * BN + half * (BN / 2);
       if (BN == 64 && !CONV && p.c_rowmajor) {  // transposed problems: a thread's results are contiguous in memory
@@ -345,6 +383,9 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
       }
     }
+    if constexpr (SPLITK) {
+      for (; cluster_syncs < 2; ++cluster_syncs) cluster_sync_all();  // a role that gave up still meets its peer
+    }
   } else {
     if constexpr (SPLIT_REGS > LAUNCH_REGS) {
       asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SPLIT_REGS));
@@ -362,8 +403,8 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const int group = t >> 7, gt = t & 127;
       constexpr int B_CHUNKS = C::B_BYTES / 16;
       int kbg = 0;  // running K-block count of this CTA
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++kbg) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        for (int kb = 0; kb < kb_count; ++kb, ++kbg) {
           if ((kbg & 1) != group) continue;
           const int st = kbg % STAGES;
           const uint32_t ph = static_cast<uint32_t>(kbg / STAGES) & 1u;
@@ -471,7 +512,7 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         gather();
       }
       int kbg = 0;  // running K-block count of this CTA
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         for (int kb = 0; kb < p.k_blocks; ++kb, ++kbg) {
           if ((kbg & 1) != group) continue;
           const int st = kbg % STAGES;
@@ -499,6 +540,13 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
   }
 
+  if constexpr (SPLITK) {
+    if (warp < 12) {  // the drain warps have passed them where they exchange the sums
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
+    }
+  }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -511,6 +559,33 @@ sgemm_3xtf32_ts_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 template <int BN, bool CONV>
 long long smem_bytes(const Tc32Params& p) {
   return Cfg<BN, CONV>::SMEM_BYTES + (CONV ? 8LL * p.k_blocks * BK : 0LL);
+}
+
+// Split-K launch: `tiles` clusters of two CTAs.
+template <int BN, bool A_MN, bool B_MN>
+cudaError_t launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int tiles,
+                          cudaStream_t stream) {
+  auto kernel = sgemm_3xtf32_ts_kernel<BN, A_MN, B_MN, false, true>;
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
+  if (attr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
+  constexpr int smem = Cfg<BN, false>::SMEM_BYTES;
+  static_assert(256 * (BN / 2) * 4 <= Cfg<BN, false>::STAGES * Cfg<BN, false>::MAIN_BYTES, "exchange area");
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(2 * tiles));
+  config.blockDim = dim3(NUM_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute cluster;
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 2;
+  cluster.val.clusterDim.y = 1;
+  cluster.val.clusterDim.z = 1;
+  config.attrs = &cluster;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, ma, mb, p);
 }
 
 template <int BN, bool A_MN, bool B_MN, bool CONV = false>

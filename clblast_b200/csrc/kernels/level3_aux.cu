@@ -279,15 +279,21 @@ __global__ void __launch_bounds__(256) im2col_kernel(ConvGeom g, int out_h, int 
     int wo = wo0;
     int h = ho0 * g.stride_h + dh, w = wo0 * g.stride_w + dw;
     int off = h * g.width + w;
-#pragma unroll 4
-    for (int pos = first; pos < plane; pos += step) {
-      T v = El<T>::zero();
-      if (static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
-          static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
-        v = im[off];
-      out[pos] = v;
-      h += h_step; w += w_step; off += off_step; wo += step_w;
-      if (wo >= g.out_w) { wo -= g.out_w; w -= w_wrap; h += g.stride_h; off += off_wrap; }
+    // eight pixels per round: all loads are issued before the first store, so eight of them are in flight per thread
+    for (int pos0 = first; pos0 < plane; pos0 += 8 * step) {
+      T v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] = El<T>::zero();
+        if (pos0 + i * step < plane && static_cast<unsigned>(h) < static_cast<unsigned>(g.height) &&
+            static_cast<unsigned>(w) < static_cast<unsigned>(g.width))
+          v[i] = im[off];
+        h += h_step; w += w_step; off += off_step; wo += step_w;
+        if (wo >= g.out_w) { wo -= g.out_w; w -= w_wrap; h += g.stride_h; off += off_wrap; }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (pos0 + i * step < plane) out[pos0 + i * step] = v[i];
     }
   }
 }
@@ -451,9 +457,7 @@ cudaError_t launch_im2col(int dtype, const ConvGeom& g, int out_h, const void* i
     return cudaErrorInvalidValue;
   const int rows_per_cta = plane >= 256 ? 1 : static_cast<int>(256 / plane);
   const unsigned groups = static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta);
-  // every thread decodes its tap and first pixel once (five integer divisions) and then walks eight images or more
-  const long long image_groups = (images + 7) / 8;
-  const dim3 grid(groups, static_cast<unsigned>(image_groups < 65535 ? image_groups : 65535));
+  const dim3 grid(groups, static_cast<unsigned>(images < 65535 ? images : 65535));
   return by_dtype(dtype, [&](auto* tag) {
     using T = typename std::remove_pointer<decltype(tag)>::type;
     im2col_kernel<T><<<grid, 256, 0, stream>>>(g, out_h, static_cast<int>(plane), rows_per_cta, static_cast<int>(rows),

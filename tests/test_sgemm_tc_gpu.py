@@ -287,7 +287,8 @@ def test_tensor_memory_and_shared_memory_variants_agree_bit_for_bit(cuda):
     root = Path(__file__).resolve().parent.parent
     runs = {}
     for switch in ("1", "0"):
-        env = dict(os.environ, B200BLAS_SGEMM_TMEM_A=switch, PYTHONPATH=str(root))
+        # split-K adds the two halves of K in another order, so it is switched off for the comparison of bits
+        env = dict(os.environ, B200BLAS_SGEMM_TMEM_A=switch, B200BLAS_SGEMM_SPLITK="0", PYTHONPATH=str(root))
         res = subprocess.run([sys.executable, "-c", _VARIANT_SCRIPT], capture_output=True, text=True, env=env, cwd=root,
                              timeout=600)
         assert res.returncode == 0, res.stderr[-2000:]
@@ -297,3 +298,17 @@ def test_tensor_memory_and_shared_memory_variants_agree_bit_for_bit(cuda):
         assert name_tm.endswith("_tmem_a") and name_tm.startswith(("tc_f32", "tc_conv")), name_tm
         assert not name_sm.endswith("_tmem_a") and name_sm.startswith(("tc_f32", "tc_conv")), name_sm
         assert digest_tm == digest_sm, (name_tm, name_sm)
+
+
+@pytest.mark.parametrize("layout,ta,tb", ALL)
+def test_few_tiles_split_k_over_a_cluster(cuda, layout, ta, tb):
+    """Problems with so few 128 x 128 tiles that half the SMs would idle run as clusters of two CTAs that take half of
+    K each and add their sums through distributed shared memory: every orientation, ragged extents, an odd number of
+    K blocks, offsets and padded leading dimensions, beta = 0 on NaN-poisoned C."""
+    rng = np.random.default_rng(31)
+    run_tc32(cuda, rng, layout, ta, tb, 1024, 1024, 1024, 0.7, 0.3)
+    assert cb.last_kernel() == "tc_f32_3xtf32_128x128x32_splitk2_tmem_a", cb.last_kernel()
+    run_tc32(cuda, rng, layout, ta, tb, 700, 520, 1064, -1.25, 0.0, offs=(8, 4, 12), pad=(4, 8, 4))  # 34 K blocks, 33.25 used
+    assert cb.last_kernel() == "tc_f32_3xtf32_128x128x32_splitk2_tmem_a", cb.last_kernel()
+    run_tc32(cuda, rng, layout, ta, tb, 516, 300, 2000 + 36, 1.0, 1.0)  # 63.6 K blocks: an odd count, ragged tail
+    assert cb.last_kernel() == "tc_f32_3xtf32_128x128x32_splitk2_tmem_a", cb.last_kernel()
