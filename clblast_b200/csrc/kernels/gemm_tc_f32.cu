@@ -696,7 +696,6 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   }();
   if (forced_ffma) return cudaErrorNotSupported;
   if (d.m < 256 || d.n < 256 || d.k < 128) return cudaErrorNotSupported;
-  if (static_cast<double>(d.m) * d.n * d.k * walk.batches < 134217728.0) return cudaErrorNotSupported;  // 512^3
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
@@ -705,6 +704,11 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
                         (d.lda % 4) || (d.ldb % 4) || d.lda * 4 >= (1LL << 40) || d.ldb * 4 >= (1LL << 40) ||
                         (walk.a_stride % 4) || (walk.b_stride % 4) || walk.a_stride * 4 >= (1LL << 40) ||
                         walk.b_stride * 4 >= (1LL << 40);
+
+  // From 256^3 multiply-adds on when TMA feeds the kernel (256^3 itself: 40 us on the CUDA-core kernel, whose four
+  // tiles leave the machine empty; split along K here), from 512^3 on when the operands have to be gathered.
+  const double work = static_cast<double>(d.m) * d.n * d.k * walk.batches;
+  if (work < ((gathered || !tmem_a_enabled()) ? 134217728.0 : 16777216.0)) return cudaErrorNotSupported;
 
   // Tile width: 256 columns amortise the operand traffic best; 128 columns give twice as many tiles and one more
   // pipeline stage, which wins while 256-wide tiles would leave SMs idle.

@@ -115,8 +115,7 @@ def test_offset_table_batches(cuda, precision, expect, layout):
     permuted = call([offs["a"][j] for j in order], offs["b"], offs["c"], batch)
     assert permuted.startswith("simt_"), permuted
     single = call(offs["a"][3:4], offs["b"][2:3], offs["c"][5:6], 1)
-    # one 384 x 512 x 136 problem is below the size at which single precision moves to the tensor cores
-    assert single.startswith(expect if precision == 16 else "simt_"), single
+    assert single.startswith(expect if precision == 16 else "tc_f32_3xtf32"), single
 
 
 @pytest.mark.parametrize("layout,ta,tb", LAYOUTS)
