@@ -243,7 +243,8 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_simt_f64(d, stream, &name);
       break;
     case 16:
-      err = d.is_conv ? launch_conv_two_step(d, stream, &name) : launch_repitched(d, stream, &name);
+      err = d.is_conv ? launch_tc_conv_f16(d, stream, &name) : launch_repitched(d, stream, &name);
+      if (err == cudaErrorNotSupported && d.is_conv) err = launch_conv_two_step(d, stream, &name);
       if (err == cudaErrorNotSupported && !d.is_conv) err = launch_tc_f16_pair(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_tc_f16(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f16(d, stream, &name);

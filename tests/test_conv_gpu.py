@@ -136,9 +136,10 @@ def test_config4_convolution_shape(cuda):
 
 @pytest.mark.parametrize("precision", (16, 64))
 def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision):
-    """Large half / double convolutions write the column matrix of a group of images to scratch and multiply it by the
-    weights on the tensor-core GEMM kernels; both kernel modes, stride, dilation and ragged extents against the fp64
-    oracle with the reference's margins."""
+    """Large half convolutions run as an implicit GEMM on tcgen05 (each thread gathers its pixel's taps into tensor
+    memory), double ones write the column matrix of a group of images to scratch and multiply it by the weights on the
+    FP64 tensor-core kernel; both kernel modes, stride, dilation, ragged extents, unaligned buffers, K that is not a
+    multiple of 8, more filters than one tile, against the fp64 oracle with the reference's margins."""
     rng = np.random.default_rng(precision)
     cases = [
         # channels, H, W, kh, kw, pad, stride, dil, num_kernels, batch
@@ -146,6 +147,9 @@ def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision
         (16, 40, 37, 3, 3, 1, 2, 1, 96, 40),
         (12, 33, 35, 5, 3, 2, 1, 2, 200, 9),
     ]
+    if precision == 16:
+        cases += [(64, 28, 28, 1, 1, 0, 1, 1, 64, 16),     # pointwise: one K block per tile
+                  (24, 50, 11, 3, 3, 1, 1, 1, 64, 16)]     # narrow rows
     for mode, (ch, h, w, kh, kw, pad, stride, dil, nk, batch) in itertools.product((151, 152), cases):
         oh, ow = oracle.conv_output_size(h, w, kh, kw, pad, pad, stride, stride, dil, dil)
         im = H.rand_buffer(rng, precision, 5 + batch * ch * h * w, -1, 1)
@@ -156,7 +160,8 @@ def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision
         st = cb.Convgemm(mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, dim, 5, dker, 3, dres, 7,
                          precision=precision)
         assert st == cb.StatusCode.kSuccess
-        assert cb.last_kernel().startswith("conv_im2col_"), cb.last_kernel()
+        # half: implicit GEMM with the im2col matrix in tensor memory; double: im2col into scratch + FP64 tensor-core GEMM
+        assert cb.last_kernel().startswith("tc_conv_f16" if precision == 16 else "conv_im2col_"), cb.last_kernel()
         want = oracle.convgemm(precision, mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, im, 5, ker,
                                3, np.zeros_like(res), 7, f64=True)
         got = H.to_host(precision, dres)
