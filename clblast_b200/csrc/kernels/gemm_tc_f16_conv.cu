@@ -15,6 +15,8 @@
 //               consecutive pixels, so a load instruction reads one contiguous run), packs them in pairs and writes 32
 //               columns with tcgen05.st. What a K row means (channel plane, tap row and column) is decoded once per
 //               launch into a table in shared memory.
+//   warp 2      asks L2 for the image rows of the tile after next (cp.async.bulk.prefetch.L2, one contiguous run per
+//               channel), so that the gather of a tile never waits for HBM
 //   warps 12-15 epilogue: tcgen05.ld of the finished accumulator (two of them alternate, so the next tile's MMAs run
 //               meanwhile), rounding to half, stores along the pixels (contiguous in the result).
 // TMEM columns: [0, 256) two accumulators, [256, 384) four slots of 32 columns for op(A).
@@ -94,8 +96,9 @@ hconv_tc_kernel(const __grid_constant__ CUtensorMap map_b, const HalfConvParams 
   auto acc_full = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 * A_SLOTS + a); };
   auto acc_empty = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 * A_SLOTS + 2 + a); };
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * A_SLOTS + 4);
-  static_assert((2 * STAGES + 2 * A_SLOTS + 4) * 8 + 8 <= 512, "barrier block");
+  static_assert((2 * STAGES + 2 * A_SLOTS + 4) * 8 + 12 <= 512, "barrier block");
   volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* const tiles_started = abort_flag + 1;  // written by the MMA lane, read by the prefetch warp
   // one entry per K row of the padded K extent: {offset of the tap from the pixel's own offset, (kh * dilation) << 16 |
   // kw * dilation}; rows beyond K get a tap row that is outside every image
   int2* const tap_table = reinterpret_cast<int2*>(reinterpret_cast<uint8_t*>(bars) + 512);
@@ -145,6 +148,7 @@ hconv_tc_kernel(const __grid_constant__ CUtensorMap map_b, const HalfConvParams 
       mbar_init(acc_empty(a), 4);
     }
     *abort_flag = 0;
+    *tiles_started = 0;
     fence_barrier_init();
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -190,6 +194,7 @@ hconv_tc_kernel(const __grid_constant__ CUtensorMap map_b, const HalfConvParams 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
+        *tiles_started = local + 1;
         if (!mbar_wait(acc_empty(acc), (static_cast<uint32_t>(local >> 1) & 1u) ^ 1u, abort_flag, 2u, p.status)) {
           ok = false;
           break;
@@ -212,6 +217,45 @@ hconv_tc_kernel(const __grid_constant__ CUtensorMap map_b, const HalfConvParams 
         }
         if (ok) umma_commit(acc_full(acc));
       }
+    }
+  } else if (warp == 2) {
+    // ---- L2 prefetch of the image rows a tile's taps touch: per channel one contiguous run of input rows ----
+    const unsigned short* const image_all = reinterpret_cast<const unsigned short*>(p.image);
+    auto prefetch_tile = [&](int tile) {
+      int tm, tn, image;
+      tile_coords(tile, tm, tn, image);
+      if (tn != 0) return;  // the filter tiles of one pixel tile read the same rows
+      const int first_pixel = tm * BM;
+      const int last_pixel = min(first_pixel + BM, p.m) - 1;
+      int h_lo = (first_pixel / p.conv.out_w) * p.conv.stride_h - p.conv.pad_h;
+      int h_hi = (last_pixel / p.conv.out_w) * p.conv.stride_h - p.conv.pad_h + (p.conv.kernel_h - 1) * p.conv.dil_h;
+      h_lo = max(h_lo, 0);
+      h_hi = min(h_hi, p.conv.height - 1);
+      if (h_hi < h_lo) return;
+      const unsigned short* const base = image_all + image * p.image_stride;
+      for (int c = lane; c < p.conv.channels; c += 32) {
+        // whole 16-byte granules that contain bytes of the run: inside the pages the run itself lies in
+        const uintptr_t begin = reinterpret_cast<uintptr_t>(base + (static_cast<long long>(c) * p.conv.height + h_lo) * p.conv.width);
+        const uintptr_t end = reinterpret_cast<uintptr_t>(base + (static_cast<long long>(c) * p.conv.height + h_hi + 1) * p.conv.width);
+        const uintptr_t from = begin & ~static_cast<uintptr_t>(15);
+        const uint32_t bytes = static_cast<uint32_t>(((end + 15) & ~static_cast<uintptr_t>(15)) - from);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(from), "r"(bytes) : "memory");
+      }
+    };
+    int local = 0;
+    if (static_cast<int>(blockIdx.x) < num_tiles) prefetch_tile(blockIdx.x);
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      // Two tiles ahead of the MMAs at most. A plain counter, not an mbarrier: this warp may fall behind without
+      // harm, and a phase bit it has missed twice would look like one it still has to wait for. Prefetching is
+      // optional, so the warp just stops when the bounded wait runs out or another role has given up.
+      const long long start = clock64();
+      bool go = true;
+      while (*tiles_started < local) {
+        __nanosleep(200);
+        if (*abort_flag || clock64() - start > kWaitCycles) { go = false; break; }
+      }
+      if (!__all_sync(0xffffffffu, go)) break;
+      if (tile + static_cast<int>(gridDim.x) < num_tiles) prefetch_tile(tile + gridDim.x);
     }
   } else if (warp >= 12) {
     // ---- epilogue: warp w reads TMEM lanes [32 (w % 4), +32) = 32 consecutive pixels, all 128 filters ----

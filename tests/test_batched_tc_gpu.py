@@ -61,6 +61,8 @@ def test_strided_batched_sgemm(cuda, layout, ta, tb):
     run_strided(cuda, rng, 32, layout, ta, tb, 520, 392, 136, 9, 1.5, 0.5, 4, 8, "tc_f32_3xtf32_128x128x32")
     # leading dimensions and strides that are not multiples of four elements: gathered operands
     run_strided(cuda, rng, 32, layout, ta, tb, 520, 392, 136, 9, -1.0, 0.0, 3, 5, "tc_f32_3xtf32_gather")
+    # few tiles in the whole batch: every tile of every problem is split along K over a cluster of two CTAs
+    run_strided(cuda, rng, 32, layout, ta, tb, 520, 392, 296, 3, 0.75, -0.5, 4, 8, "tc_f32_3xtf32_128x128x32_splitk2")
 
 
 def test_strided_batched_sgemm_on_cta_pairs(cuda):
