@@ -239,7 +239,8 @@ cudaError_t dispatch(const GemmDesc& d, cudaStream_t stream) {
       if (err == cudaErrorNotSupported) err = launch_simt_f32(d, stream, &name);
       break;
     case 64:
-      err = d.is_conv ? launch_conv_two_step(d, stream, &name) : launch_dmma_f64(d, stream, &name);
+      err = d.is_conv ? launch_dmma_conv_f64(d, stream, &name) : launch_dmma_f64(d, stream, &name);
+      if (err == cudaErrorNotSupported && d.is_conv) err = launch_conv_two_step(d, stream, &name);
       if (err == cudaErrorNotSupported) err = launch_simt_f64(d, stream, &name);
       break;
     case 16:

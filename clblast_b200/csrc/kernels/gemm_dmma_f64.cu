@@ -26,7 +26,9 @@ constexpr int NT = 256;
 constexpr int LDS_A = BM + 4, LDS_B = BN + 4;  // row stride = 4 (mod 16) doubles: fragment loads are conflict-free
 constexpr int SMEM_BYTES = 2 * BK * (LDS_A + LDS_B) * 8;  // double-buffered A and B tiles, above the 48 KB static limit
 
-template <bool A_KC, bool B_KC>
+// CONV: op(A) is the implicit im2col matrix of image bz (rows = output pixels, contiguous along the pixels), gathered
+// with the loader of the CUDA-core convolution (TileStager::fetch_conv); B holds the weights [filter][k].
+template <bool A_KC, bool B_KC, bool CONV = false>
 __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<double> p) {
   using Tr = TraitsF64;
   using StA = TileStager<Tr, BM, BK, NT, A_KC>;
@@ -72,8 +74,15 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
       for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
 
     double ra[StA::NV][Tr::VEC], rb[StB::NV][Tr::VEC];
+    int conv_h0[CONV ? StA::NV : 1][CONV ? Tr::VEC : 1];
+    int conv_w0[CONV ? StA::NV : 1][CONV ? Tr::VEC : 1];
+    if constexpr (CONV) StA::conv_pixels(conv_h0, conv_w0, p.conv, m0, m_rem, tid);
     auto fetch_tiles = [&](long long k0) {
-      StA::fetch(ra, a_base, p.lda, m0, k0, m_rem, p.k - k0, a_vec_ok, tid);
+      if constexpr (CONV) {
+        StA::fetch_conv(ra, a_base, p.conv, conv_h0, conv_w0, k0, p.k - k0, tid);
+      } else {
+        StA::fetch(ra, a_base, p.lda, m0, k0, m_rem, p.k - k0, a_vec_ok, tid);
+      }
       StB::fetch(rb, b_base, p.ldb, n0, k0, n_rem, p.k - k0, b_vec_ok, tid);
     };
     fetch_tiles(0);
@@ -138,7 +147,7 @@ __global__ void __launch_bounds__(NT, 1) gemm_dmma_kernel(const SimtParams<doubl
   }
 }
 
-template <bool A_KC, bool B_KC>
+template <bool A_KC, bool B_KC, bool CONV = false>
 cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
   SimtParams<double> p;
   p.a = d.a; p.b = d.b; p.c = d.c;
@@ -162,9 +171,9 @@ cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
   const long long max_grid = 1LL << 30;
   const unsigned grid = static_cast<unsigned>(p.total_tiles < max_grid ? p.total_tiles : max_grid);
   const cudaError_t e =
-      cudaFuncSetAttribute(gemm_dmma_kernel<A_KC, B_KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      cudaFuncSetAttribute(gemm_dmma_kernel<A_KC, B_KC, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  gemm_dmma_kernel<A_KC, B_KC><<<grid, NT, SMEM_BYTES, stream>>>(p);
+  gemm_dmma_kernel<A_KC, B_KC, CONV><<<grid, NT, SMEM_BYTES, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -183,6 +192,22 @@ cudaError_t launch_dmma_f64(const GemmDesc& d, cudaStream_t stream, const char**
   *name = "dmma_f64_128x128x16";
   if (d.a_kcontig) return d.b_kcontig ? go<true, true>(d, stream) : go<true, false>(d, stream);
   return d.b_kcontig ? go<false, true>(d, stream) : go<false, false>(d, stream);
+}
+
+// Double-precision Convgemm as an implicit GEMM on the FP64 tensor-core path: no column matrix in memory. Replaces the
+// reference's XconvgemmNormal / XconvgemmFlip for large problems (src/kernels/levelx/xconvgemm_part2.opencl:27-336).
+cudaError_t launch_dmma_conv_f64(const GemmDesc& d, cudaStream_t stream, const char** name) {
+  if (d.dtype != 64 || !d.is_conv || d.force_small) return cudaErrorNotSupported;
+  static const bool disabled = [] {  // B200BLAS_CONV=simt | im2col: the CUDA-core kernel / the two-step route
+    const char* v = std::getenv("B200BLAS_CONV");
+    return v != nullptr && (std::strcmp(v, "simt") == 0 || std::strcmp(v, "im2col") == 0);
+  }();
+  if (disabled) return cudaErrorNotSupported;
+  const long long tiles = ((d.m + BM - 1) / BM) * ((d.n + BN - 1) / BN) * d.batch;
+  if (d.m < 96 || d.n < 32 || d.k < 32 || tiles < 120) return cudaErrorNotSupported;
+  if (d.m > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;  // the loader keeps pixels and K rows in int
+  *name = "conv_dmma_f64_128x128x16";
+  return go<false, true, true>(d, stream);
 }
 
 }  // namespace b200

@@ -49,6 +49,8 @@ cudaError_t launch_complex_on_real(const GemmDesc& d, cudaStream_t stream, const
 cudaError_t launch_conv_two_step(const GemmDesc& d, cudaStream_t stream, const char** name);
 // Half-precision Convgemm as an implicit GEMM with the im2col matrix in tensor memory (gemm_tc_f16_conv.cu).
 cudaError_t launch_tc_conv_f16(const GemmDesc& d, cudaStream_t stream, const char** name);
+// Double-precision Convgemm as an implicit GEMM on the FP64 mma.sync kernel (gemm_dmma_f64.cu).
+cudaError_t launch_dmma_conv_f64(const GemmDesc& d, cudaStream_t stream, const char** name);
 
 // Large half / single GEMMs with operands TMA cannot address: the offending operands are copied once into scratch with
 // an aligned pitch and the kernels above run on the copies (csrc/repitch.cpp). Same contract as launch_tc_f16.

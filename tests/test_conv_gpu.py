@@ -137,8 +137,7 @@ def test_config4_convolution_shape(cuda):
 @pytest.mark.parametrize("precision", (16, 64))
 def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision):
     """Large half convolutions run as an implicit GEMM on tcgen05 (each thread gathers its pixel's taps into tensor
-    memory), double ones write the column matrix of a group of images to scratch and multiply it by the weights on the
-    FP64 tensor-core kernel; both kernel modes, stride, dilation, ragged extents, unaligned buffers, K that is not a
+    memory), double ones as an implicit GEMM on the FP64 mma.sync kernel; both kernel modes, stride, dilation, ragged extents, unaligned buffers, K that is not a
     multiple of 8, more filters than one tile, against the fp64 oracle with the reference's margins."""
     rng = np.random.default_rng(precision)
     cases = [
@@ -160,8 +159,8 @@ def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision
         st = cb.Convgemm(mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, dim, 5, dker, 3, dres, 7,
                          precision=precision)
         assert st == cb.StatusCode.kSuccess
-        # half: implicit GEMM with the im2col matrix in tensor memory; double: im2col into scratch + FP64 tensor-core GEMM
-        assert cb.last_kernel().startswith("tc_conv_f16" if precision == 16 else "conv_im2col_"), cb.last_kernel()
+        # half: implicit GEMM with the im2col matrix in tensor memory; double: implicit GEMM on the FP64 mma.sync kernel
+        assert cb.last_kernel().startswith("tc_conv_f16" if precision == 16 else "conv_dmma_f64"), cb.last_kernel()
         want = oracle.convgemm(precision, mode, ch, h, w, kh, kw, pad, pad, stride, stride, dil, dil, nk, batch, im, 5, ker,
                                3, np.zeros_like(res), 7, f64=True)
         got = H.to_host(precision, dres)
@@ -170,3 +169,42 @@ def test_half_and_double_convolutions_on_the_tensor_core_kernels(cuda, precision
         assert bad == 0, (mode, ch, h, w, worst)
         k = ch * kh * kw
         assert worst <= (2e-3 if precision == 16 else 2.0 ** -48 * k), (worst, k)
+
+
+_TWO_STEP_SCRIPT = r"""
+import hashlib
+import numpy as np
+import torch
+import clblast_b200 as cb
+g = torch.Generator(device="cuda").manual_seed(9)
+for dt in (torch.float16, torch.float64):
+    ch, h, w, nk, batch = 32, 40, 37, 96, 24
+    im = ((torch.rand(batch * ch * h * w, generator=g, device="cuda") * 2 - 1)).to(dt)
+    ker = ((torch.rand(nk * ch * 9, generator=g, device="cuda") * 2 - 1) * 0.1).to(dt)
+    res = torch.zeros(batch * nk * h * w, device="cuda", dtype=dt)
+    assert cb.Convgemm(151, ch, h, w, 3, 3, 1, 1, 1, 1, 1, 1, nk, batch, im, 0, ker, 0, res, 0) == 0
+    torch.cuda.synchronize()
+    want = torch.nn.functional.conv2d(im.view(batch, ch, h, w).double(), ker.view(nk, ch, 3, 3).double(), padding=1)
+    err = (res.view(batch, nk, h, w).double() - want).abs().max().item()
+    print(cb.last_kernel(), err)
+"""
+
+
+def test_two_step_route_on_request(cuda):
+    """B200BLAS_CONV=im2col sends half / double convolutions through im2col into scratch and one strided-batched GEMM
+    on the tensor-core kernels (the reference's second method, src/routines/levelx/xconvgemm.cpp:96-112); checked
+    against a double-precision convolution in a process of its own (the switch is read once)."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, B200BLAS_CONV="im2col", PYTHONPATH=str(root))
+    res = subprocess.run([sys.executable, "-c", _TWO_STEP_SCRIPT], capture_output=True, text=True, env=env, cwd=root,
+                         timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [line.split() for line in res.stdout.strip().splitlines()]
+    assert len(lines) == 2, res.stdout
+    assert lines[0][0].startswith("conv_im2col_tc_f16") and float(lines[0][1]) < 2e-2, lines[0]
+    assert lines[1][0].startswith("conv_im2col_dmma_f64") and float(lines[1][1]) < 1e-12, lines[1]
