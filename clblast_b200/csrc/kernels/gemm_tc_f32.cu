@@ -715,7 +715,11 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
   const int device_sms = sm_count();
   if (device_sms <= 0) return cudaErrorNotSupported;
   const long long tiles_wide = ((d.m + BM - 1) / BM) * ((d.n + 255) / 256) * walk.batches;
-  int bn = (!gathered && tiles_wide >= 2LL * device_sms) ? 256 : 128;
+  static const bool forced_128 = [] {  // B200BLAS_SGEMM=single128: no CTA pairs and 128-column tiles whatever the size
+    const char* v = std::getenv("B200BLAS_SGEMM");
+    return v != nullptr && std::strcmp(v, "single128") == 0;
+  }();
+  int bn = (!gathered && !forced_128 && tiles_wide >= 2LL * device_sms) ? 256 : 128;
   // Small problems: when twice as many tiles still fit the machine in one wave, 64-column tiles put twice as many
   // SMs to work (1024^3: 64 -> 128 CTAs, 56 -> 66 TFLOP/s).
   const long long tiles_128 = ((d.m + BM - 1) / BM) * ((d.n + 127) / 128) * walk.batches;

@@ -405,7 +405,7 @@ cudaError_t launch_tc_f32_pair(const GemmDesc& d, cudaStream_t stream, const cha
   // B200BLAS_SGEMM=ffma forces the CUDA-core kernel, =single the one-CTA-per-tile tensor-core kernels
   static const bool disabled = [] {
     const char* v = std::getenv("B200BLAS_SGEMM");
-    return v != nullptr && (std::strcmp(v, "ffma") == 0 || std::strcmp(v, "single") == 0);
+    return v != nullptr && (std::strcmp(v, "ffma") == 0 || std::strcmp(v, "single") == 0 || std::strcmp(v, "single128") == 0);
   }();
   if (disabled) return cudaErrorNotSupported;
   if (d.m < 512 || d.n < 256 || d.k < 128) return cudaErrorNotSupported;
