@@ -13,6 +13,7 @@
 // Fragments (m8n8k4, A row-major, B column-major): lane = 4*g + t holds A(g, t), B(t, g), C(g, 2t) and C(g, 2t+1).
 #include "gemm_simt.cuh"
 #include "launchers.h"
+#include "../runtime_state.h"
 
 #include <cstdlib>
 #include <cstring>
@@ -170,8 +171,7 @@ cudaError_t go(const GemmDesc& d, cudaStream_t stream) {
   p.conv = d.conv;
   const long long max_grid = 1LL << 30;
   const unsigned grid = static_cast<unsigned>(p.total_tiles < max_grid ? p.total_tiles : max_grid);
-  const cudaError_t e =
-      cudaFuncSetAttribute(gemm_dmma_kernel<A_KC, B_KC, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(gemm_dmma_kernel<A_KC, B_KC, CONV>), SMEM_BYTES);
   if (e != cudaSuccess) return e;
   gemm_dmma_kernel<A_KC, B_KC, CONV><<<grid, NT, SMEM_BYTES, stream>>>(p);
   return cudaGetLastError();

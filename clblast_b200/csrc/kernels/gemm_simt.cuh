@@ -22,6 +22,7 @@
 #include <stdint.h>
 
 #include "gemm_desc.h"
+#include "../runtime_state.h"
 
 namespace b200 {
 
@@ -505,8 +506,8 @@ struct SimtLauncher {
     constexpr int NT = (BM / TM) * (BN / TN) * GROUPS;
     constexpr size_t SMEM = sizeof(S) * 2 * BK * ((BM + 4) + (BN + 4)) * GROUPS;
     auto kernel = gemm_simt_kernel<Tr, BM, BN, BK, TM, TN, A_KC, B_KC, CONV, MINB, GROUPS>;
-    if (SMEM > 48 * 1024) {  // per-context opt-in, repeated per launch because contexts come and go
-      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (SMEM > 48 * 1024) {  // per-context opt-in (remembered per context)
+      const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), static_cast<int>(SMEM));
       if (e != cudaSuccess) return e;
     }
     kernel<<<grid, NT, SMEM, stream>>>(p);

@@ -271,8 +271,8 @@ struct SmallLauncher {
     constexpr int SMEM = GROUPS * SETS * L::SET_FLOATS * static_cast<int>(sizeof(float));
     static_assert(CTAS * SMEM <= 226 * 1024, "the resident CTAs must fit the shared memory of one SM");
     auto kernel = gemm_small_batched_kernel<BM, BN, KMAX, TM, TN, GROUPS, SETS, CTAS, A_KC, B_KC>;
-    {  // per-context attribute; contexts come and go, so it is set before every launch
-      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    {  // per-context attribute (remembered per context)
+      const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), SMEM);
       if (e != cudaSuccess) return e;
     }
     const long long ctas = (p.batch + GROUPS - 1) / GROUPS;

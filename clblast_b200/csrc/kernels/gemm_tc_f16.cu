@@ -277,8 +277,8 @@ template <bool A_MN, bool B_MN>
 cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p,
                            int grid, cudaStream_t stream) {
   auto kernel = hgemm_tc_kernel<A_MN, B_MN>;
-  // per-context opt-in to more than 48 KB of dynamic shared memory, repeated per launch (contexts come and go)
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  // per-context opt-in to more than 48 KB of dynamic shared memory (remembered per context)
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), SMEM_BYTES);
   if (e != cudaSuccess) return e;
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, p);
   return cudaGetLastError();

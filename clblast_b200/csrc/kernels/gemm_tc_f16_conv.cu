@@ -447,8 +447,7 @@ cudaError_t launch_tc_conv_f16(const GemmDesc& d, cudaStream_t stream, const cha
   int sms = device_sms;
   if (sm_budget() > 0 && sm_budget() < sms) sms = sm_budget();
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  const cudaError_t e =
-      cudaFuncSetAttribute(hconv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(hconv_tc_kernel), static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   *name = "tc_conv_f16_128x128x64_tmem_a";
   hconv_tc_kernel<<<grid, NUM_THREADS, static_cast<size_t>(smem), stream>>>(map_b, p);

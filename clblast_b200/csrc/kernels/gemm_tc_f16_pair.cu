@@ -309,7 +309,7 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const C
   if (sm_budget() > 0 && sm_budget() / 2 < pairs) pairs = sm_budget() / 2;
   if (pairs <= 0) return cudaErrorNotSupported;
   if (tiles < pairs) pairs = static_cast<int>(tiles);
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), SMEM_BYTES);
   if (e != cudaSuccess) return e;
   kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, p);
   return cudaGetLastError();

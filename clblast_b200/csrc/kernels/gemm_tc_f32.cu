@@ -655,11 +655,10 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const T
   auto kernel = sgemm_3xtf32_kernel<BN, A_MN, B_MN, MODE>;
   // The kernel re-balances registers between its warpgroups; that only works while the registers the compiler gave
   // each thread at launch cover the budgets it asks for. Refuse (the CUDA-core kernel runs instead) otherwise.
-  cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
-  if (attr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+  int regs = 0;
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), Cfg<BN>::SMEM_BYTES, &regs);
   if (e != cudaSuccess) return e;
+  if (regs < LAUNCH_REGS) return cudaErrorNotSupported;
   kernel<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ma, mb, p);
   return cudaGetLastError();
 }
@@ -839,8 +838,12 @@ cudaError_t launch_tc_f32_narrow(const GemmDesc& d, cudaStream_t stream, const c
   constexpr int BN = 64;
   if (d.m > BN || d.m < 16 || d.n < 64 || d.k < 32 || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const long long tiles = ((d.n + BM - 1) / BM) * walk.batches;
-  if (tiles < sm_count() || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
-  if (static_cast<double>(d.m) * d.n * d.k * walk.batches < 134217728.0) return cudaErrorNotSupported;
+  // A single wide problem of few rows (the 64-row products of the blocked triangular solve: 64 x 8192 x 64 takes 13 us
+  // on the CUDA-core kernel) is worth the tensor cores from a quarter of the machine on; batches, which the streaming
+  // kernel serves bit-identically to the reference order, only when they fill it.
+  const bool single = walk.batches == 1 && tmem_a_enabled();
+  if (tiles < (single ? 32 : sm_count()) || tiles > 0x7FFFFFFF) return cudaErrorNotSupported;
+  if (static_cast<double>(d.m) * d.n * d.k * walk.batches < (single ? 16777216.0 : 134217728.0)) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (d.lda % 4) || (d.ldb % 4) ||

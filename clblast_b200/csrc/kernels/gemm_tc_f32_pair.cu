@@ -380,17 +380,15 @@ cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const P
   auto kernel = sgemm_3xtf32_pair_kernel<A_MN, B_MN>;
   // The register re-balancing between warpgroups only works while the registers given to each thread at launch
   // cover the budgets asked for; otherwise leave the problem to the single-CTA kernels.
-  cudaFuncAttributes fattr;
-  if (cudaFuncGetAttributes(&fattr, kernel) != cudaSuccess) return cudaErrorNotSupported;
-  if (fattr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
+  int regs = 0;
+  if (kernel_ready(reinterpret_cast<const void*>(kernel), SMEM_BYTES, &regs) != cudaSuccess) return cudaErrorNotSupported;
+  if (regs < LAUNCH_REGS) return cudaErrorNotSupported;
   static std::atomic<int> pairs_of_device[kMaxDevices];
   int pairs = per_device(pairs_of_device, &resident_pairs<A_MN, B_MN>);
   if (pairs <= 0) return cudaErrorNotSupported;
   if (sm_budget() > 0 && sm_budget() / 2 < pairs) pairs = sm_budget() / 2;
   if (pairs <= 0) return cudaErrorNotSupported;
   if (tiles < pairs) pairs = static_cast<int>(tiles);
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return e;
   kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, p);
   return cudaGetLastError();
 }

@@ -566,13 +566,12 @@ template <int BN, bool A_MN, bool B_MN>
 cudaError_t launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int tiles,
                           cudaStream_t stream) {
   auto kernel = sgemm_3xtf32_ts_kernel<BN, A_MN, B_MN, false, true>;
-  cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
-  if (attr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;
   constexpr int smem = Cfg<BN, false>::SMEM_BYTES;
   static_assert(256 * (BN / 2) * 4 <= Cfg<BN, false>::STAGES * Cfg<BN, false>::MAIN_BYTES, "exchange area");
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  int regs = 0;
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), smem, &regs);
   if (e != cudaSuccess) return e;
+  if (regs < LAUNCH_REGS) return cudaErrorNotSupported;  // the register re-balancing needs the full pool
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(2 * tiles));
   config.blockDim = dim3(NUM_THREADS);
@@ -591,13 +590,12 @@ cudaError_t launch_splitk(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
 template <int BN, bool A_MN, bool B_MN, bool CONV = false>
 cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const Tc32Params& p, int grid, cudaStream_t stream) {
   auto kernel = sgemm_3xtf32_ts_kernel<BN, A_MN, B_MN, CONV>;
-  cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return cudaErrorNotSupported;
-  if (attr.numRegs < LAUNCH_REGS) return cudaErrorNotSupported;  // the register re-balancing needs the full pool
   const long long smem = smem_bytes<BN, CONV>(p);
   if (smem > 227 * 1024) return cudaErrorNotSupported;
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  int regs = 0;
+  const cudaError_t e = kernel_ready(reinterpret_cast<const void*>(kernel), static_cast<int>(smem), &regs);
   if (e != cudaSuccess) return e;
+  if (regs < LAUNCH_REGS) return cudaErrorNotSupported;  // the register re-balancing needs the full pool
   kernel<<<grid, NUM_THREADS, static_cast<size_t>(smem), stream>>>(ma, mb, p);
   return cudaGetLastError();
 }

@@ -1,5 +1,9 @@
 #include "runtime_state.h"
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include <cstring>
 #include <mutex>
 
@@ -49,6 +53,41 @@ int context_key(unsigned long long* key) {
   }
   *key = k;
   return 0;
+}
+
+cudaError_t kernel_ready(const void* func, int smem_bytes, int* regs) {
+  struct Entry { int smem; int regs; };
+  static std::mutex guard;
+  static std::map<std::pair<unsigned long long, const void*>, Entry> table;  // (context, kernel)
+  unsigned long long ctx = 0;
+  if (context_key(&ctx) != 0) ctx = 0;  // no key: fall through to the runtime calls every time
+  {
+    std::lock_guard<std::mutex> lock(guard);
+    const auto it = table.find({ctx, func});
+    if (ctx != 0 && it != table.end() && it->second.smem >= smem_bytes && (regs == nullptr || it->second.regs > 0)) {
+      if (regs) *regs = it->second.regs;
+      return cudaSuccess;
+    }
+  }
+  Entry e = {smem_bytes, 0};
+  if (regs) {
+    cudaFuncAttributes attr;
+    const cudaError_t ga = cudaFuncGetAttributes(&attr, func);
+    if (ga != cudaSuccess) return ga;
+    e.regs = attr.numRegs;
+    *regs = attr.numRegs;
+  }
+  if (smem_bytes > 48 * 1024) {
+    const cudaError_t sa = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (sa != cudaSuccess) return sa;
+  }
+  if (ctx != 0) {
+    std::lock_guard<std::mutex> lock(guard);
+    Entry& slot = table[{ctx, func}];
+    if (slot.smem < e.smem) slot.smem = e.smem;
+    if (e.regs > 0) slot.regs = e.regs;
+  }
+  return cudaSuccess;
 }
 
 namespace {

@@ -22,6 +22,11 @@ int per_device(std::atomic<int> (&table)[kMaxDevices], int (*compute)());
 // Returns 0 and stores the key, or a CUresult / cudaError value.
 int context_key(unsigned long long* key);
 
+// Raises a kernel's dynamic shared-memory limit to `smem_bytes` unless this context already has it at least that high,
+// and returns the kernel's register count in `regs` when asked. The runtime calls behind this take a few microseconds
+// per launch otherwise, which is what a small problem's kernel takes. `func` is the kernel's host function pointer.
+cudaError_t kernel_ready(const void* func, int smem_bytes, int* regs = nullptr);
+
 // Status block written by the tensor-core kernels when a bounded wait expires: word 0 = code (1 producer,
 // 2 accumulator-free, 3 operands-ready, 4 accumulator-ready, 5 raw-tile, 6 old-C block), word 1 = block index,
 // word 2 = barrier address. It lives in a page of host memory inside the library image that is registered with the
