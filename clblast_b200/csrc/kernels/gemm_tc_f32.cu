@@ -694,7 +694,9 @@ cudaError_t launch_tc_f32(const GemmDesc& d, cudaStream_t stream, const char** n
     return v != nullptr && std::strcmp(v, "ffma") == 0;
   }();
   if (forced_ffma) return cudaErrorNotSupported;
-  if (d.m < 256 || d.n < 256 || d.k < 128) return cudaErrorNotSupported;
+  // one full tile row at least (with op(A) in tensor memory; 256 x 256 for the shared-memory kernels)
+  const long long least = tmem_a_enabled() ? 128 : 256;
+  if (d.m < least || d.n < least || d.k < 128) return cudaErrorNotSupported;
   if (d.m > 0x7FFFFFFF || d.n > 0x7FFFFFFF || d.k > 0x7FFFFFFF) return cudaErrorNotSupported;
   const float* a = static_cast<const float*>(d.a) + d.a_off;
   const float* b = static_cast<const float*>(d.b) + d.b_off;
