@@ -31,6 +31,7 @@ import re
 import statistics
 import subprocess
 import sys
+import threading
 import time
 from pathlib import Path
 
@@ -163,28 +164,47 @@ class ClockSampler:
     def __init__(self, index):
         self.index = index
         self.proc = None
+        self.lines = []
+        self.reader = None
 
     def start(self):
+        """Starts nvidia-smi and returns once its first sample has arrived (several ranks starting it at once take a
+        few hundred milliseconds), so that the samples that follow fall into the region being timed."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "10"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append((time.monotonic(), line))
+
+        self.reader = threading.Thread(target=pump, daemon=True)
+        self.reader.start()
+        deadline = time.monotonic() + 5.0
+        while not self.lines and time.monotonic() < deadline and self.proc.poll() is None:
+            time.sleep(0.01)
+        self.begin = time.monotonic()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        if self.reader is not None:
+            self.reader.join(timeout=2)
+        # the samples taken since start() returned; all of them when the region was shorter than one sampling period
+        chosen = [line for stamp, line in self.lines if stamp >= self.begin] or [line for _, line in self.lines]
         sm, smax, reasons, power = [], [], set(), []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.splitlines():
+        for line in chosen:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -690,15 +710,19 @@ def main():
     bcast = {"bufs": None, "cur": 0, "work": None, "fan": None}
     bcast_how = None
     if replicate_b:
-        bcast["bufs"] = [t["b"], torch.empty_like(t["b"])]
+        # Three ring slots for the copy-engine tree: the copy of step s + 3 into a slot may start as soon as the GEMM of
+        # step s is done, which leaves it two GEMMs' time to cross up to three hops while copies share HBM and NVLink
+        # with the running GEMMs (with two slots and eight ranks the leaves waited: 0.87 ms per step against 0.77).
+        bcast["bufs"] = [t["b"]] + [torch.empty_like(t["b"]) for _ in range(1 if use_nccl else 2)]
         dist.broadcast(bcast["bufs"][0], src=0)     # set-up, outside every timed region
-        bcast["bufs"][1].copy_(bcast["bufs"][0])
+        for extra in bcast["bufs"][1:]:
+            extra.copy_(bcast["bufs"][0])
         torch.cuda.synchronize()
         if not use_nccl:
             try:
                 from clblast_b200.multi_gpu import CopyEngineFanout
                 bcast["fan"] = CopyEngineFanout(dist, bcast["bufs"], root=0)
-                bcast_how = "binomial tree of cudaMemcpyAsync peer copies (copy engines), double buffered"
+                bcast_how = "binomial tree of cudaMemcpyAsync peer copies (copy engines), three ring slots"
             except Exception as exc:
                 flag = torch.tensor([1], device="cuda")
                 print(f"note: copy-engine fan-out unavailable on rank {rank} ({exc}); falling back to NCCL", file=sys.stderr)
