@@ -1,0 +1,67 @@
+"""The index arithmetic of the tensor-memory convolution kernels, restated in numpy and checked against the oracle's
+im2col (itself pinned to the reference's im2col kernel source, src/kernels/levelx/im2col.opencl:24-62).
+
+The kernels (clblast_b200/csrc/kernels/gemm_tc_f32_ts.cuh, gemm_tc_f16_conv.cu) decode every K row once per launch
+into a table entry {offset of the tap from the pixel's own offset, (kh * dilation) << 16 | kw * dilation}; a gather
+thread owns one output pixel, keeps h0 = ho * stride - pad, w0 = wo * stride - pad and pix_off = h0 * W + w0, and loads
+image[entry.x + pix_off] when both (unsigned) h0 + dh < H and w0 + dw < W. K rows beyond K get dh = 0x7FFF, pixels
+beyond the image h0 = -0x20000000: neither can pass the test. This file checks that recipe, the sentinels included, on
+random geometries; it runs on the CPU (the kernels themselves are checked against the oracle on the GPU)."""
+import numpy as np
+import pytest
+
+from oracle import cpu_oracle as oracle
+
+
+def tap_table(channels, height, width, kh_n, kw_n, dil_h, dil_w, flip, k_blocks, bk):
+    khw = kh_n * kw_n
+    k_total = channels * khw
+    off = np.zeros(k_blocks * bk, dtype=np.int64)
+    packed = np.full(k_blocks * bk, 0x7FFF0000, dtype=np.int64)
+    for kg in range(min(k_total, k_blocks * bk)):
+        c, k2 = divmod(kg, khw)
+        kh, kw = divmod(k2, kw_n)
+        if flip:
+            kh, kw = kh_n - 1 - kh, kw_n - 1 - kw
+        dh, dw = kh * dil_h, kw * dil_w
+        off[kg] = (c * height + dh) * width + dw
+        packed[kg] = (dh << 16) | dw
+    return off, packed
+
+
+def gathered_matrix(image, channels, height, width, kh_n, kw_n, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, flip, bk,
+                    tile_pixels=128):
+    oh, ow = oracle.conv_output_size(height, width, kh_n, kw_n, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w)
+    m, k_total = oh * ow, channels * kh_n * kw_n
+    k_blocks = -(-k_total // bk)
+    off, packed = tap_table(channels, height, width, kh_n, kw_n, dil_h, dil_w, flip, k_blocks, bk)
+    tiles = -(-m // tile_pixels)
+    pixels = np.arange(tiles * tile_pixels)                      # the last tile runs past the image
+    ho, wo = pixels // ow, pixels % ow
+    h_first = ho * stride_h - pad_h
+    w0 = wo * stride_w - pad_w
+    pix_off = h_first * width + w0
+    h0 = np.where(pixels < m, h_first, -0x20000000)
+    dh, dw = packed >> 16, packed & 0xFFFF
+    hh = h0[None, :] + dh[:, None]
+    ww = w0[None, :] + dw[:, None]
+    inside = (hh >= 0) & (hh < height) & (ww >= 0) & (ww < width)   # the unsigned compares of the kernels
+    index = off[:, None] + pix_off[None, :]
+    assert index[inside].min(initial=0) >= 0 and index[inside].max(initial=0) < image.size, "a load would leave the image"
+    return np.where(inside, image[np.clip(index, 0, image.size - 1)], 0), m, k_total
+
+
+@pytest.mark.parametrize("bk", (32, 64))
+def test_tap_table_and_predicates_reproduce_im2col(bk):
+    rng = np.random.default_rng(bk)
+    cases = [(3, 9, 11, 3, 3, 1, 1, 1, 1, 1, 1), (5, 20, 7, 5, 3, 2, 0, 2, 1, 1, 2), (2, 6, 6, 1, 1, 0, 0, 1, 1, 1, 1),
+             (4, 13, 17, 3, 2, 0, 2, 3, 2, 2, 1), (1, 5, 40, 2, 7, 1, 3, 1, 3, 1, 1), (7, 8, 8, 3, 3, 2, 2, 1, 1, 2, 2)]
+    for ch, h, w, kh_n, kw_n, pad_h, pad_w, sh, sw, dh, dw in cases:
+        image = rng.standard_normal(ch * h * w).astype(np.float32)
+        for mode in (151, 152):
+            got, m, k_total = gathered_matrix(image, ch, h, w, kh_n, kw_n, pad_h, pad_w, sh, sw, dh, dw, mode == 152, bk)
+            want = oracle.im2col(mode, ch, h, w, kh_n, kw_n, pad_h, pad_w, sh, sw, dh, dw, image, 0,
+                                 np.zeros(k_total * m, dtype=np.float32), 0).reshape(k_total, m)
+            assert np.array_equal(got[:k_total, :m], want), (ch, h, w, kh_n, kw_n, mode)
+            assert not got[k_total:].any(), "K rows of the padding must read as zero"
+            assert not got[:, m:].any(), "pixels beyond the image must read as zero"
