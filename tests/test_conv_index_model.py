@@ -65,3 +65,43 @@ def test_tap_table_and_predicates_reproduce_im2col(bk):
             assert np.array_equal(got[:k_total, :m], want), (ch, h, w, kh_n, kw_n, mode)
             assert not got[k_total:].any(), "K rows of the padding must read as zero"
             assert not got[:, m:].any(), "pixels beyond the image must read as zero"
+
+
+def test_im2col_kernel_walks_pixels_with_additions_only():
+    """im2col_kernel (clblast_b200/csrc/kernels/level3_aux.cu) gives each thread every 256th pixel of a row of the
+    column matrix (or one pixel, when several short rows share a CTA) and moves row, column and offset of the tap by
+    constants, with one correction when the output column wraps. The same walk in Python must land on the pixels the
+    direct formula gives."""
+    for height, width in ((56, 56), (7, 7), (20, 33), (300, 5), (5, 300), (17, 16)):
+        for k, pad, (sh, sw), (dh_, dw_) in ((1, 0, (1, 1), (1, 1)), (3, 1, (2, 1), (2, 1)), (3, 0, (3, 2), (1, 1)),
+                                             (3, 1, (1, 1), (1, 1))):
+            oh, ow = oracle.conv_output_size(height, width, k, k, pad, pad, sh, sw, dh_, dw_)
+            if oh <= 0 or ow <= 0:
+                continue
+            plane = oh * ow
+            rows_per_cta = 1 if plane >= 256 else 256 // plane
+            for kh in range(k):
+                for kw in range(k):
+                    dh, dw = kh * dh_ - pad, kw * dw_ - pad
+                    for tid in range(256):
+                        local = tid // plane if rows_per_cta > 1 else 0
+                        if local >= rows_per_cta:
+                            continue
+                        first = tid - local * plane if rows_per_cta > 1 else tid
+                        step = plane if rows_per_cta > 1 else 256
+                        step_h, step_w = divmod(step, ow)
+                        ho0, wo0 = divmod(first, ow)
+                        h_step, w_step = step_h * sh, step_w * sw
+                        off_step = h_step * width + w_step
+                        w_wrap = ow * sw
+                        off_wrap = sh * width - w_wrap
+                        wo, h, w = wo0, ho0 * sh + dh, wo0 * sw + dw
+                        off = h * width + w
+                        pos = first
+                        while pos < plane:
+                            ho_d, wo_d = divmod(pos, ow)
+                            assert (h, w, off) == (ho_d * sh + dh, wo_d * sw + dw, (ho_d * sh + dh) * width + wo_d * sw + dw)
+                            h, w, off, wo = h + h_step, w + w_step, off + off_step, wo + step_w
+                            if wo >= ow:
+                                wo, w, h, off = wo - ow, w - w_wrap, h + sh, off + off_wrap
+                            pos += step
