@@ -137,6 +137,8 @@ int main() {
               g_filter_options ? "the reference's options minus '-cl-std=CL1.1', which NVRTC rejects (status -2040 with the stock options)"
                                : "stock");
   report("sgemm_1024", gemm_case<float>(Layout::kRowMajor, 1024, 1024, 1024, 0.7f, 0.3f, 0, ctx, dev, 20), 2.0 * 1024 * 1024 * 1024);
+  report("sgemm_1000", gemm_case<float>(Layout::kColMajor, 1000, 1000, 1000, 1.5f, 0.5f, 16, ctx, dev, 20), 2.0 * 1000 * 1000 * 1000);
+  report("sgemm_2048", gemm_case<float>(Layout::kColMajor, 2048, 2048, 2048, 1.5f, 0.5f, 16, ctx, dev, 10), 2.0 * 2048 * 2048 * 2048);
   report("sgemm_4096", gemm_case<float>(Layout::kColMajor, 4096, 4096, 4096, 1.5f, 0.5f, 16, ctx, dev, 10), 2.0 * 4096 * 4096 * 4096);
   report("sgemm_ragged", gemm_case<float>(Layout::kColMajor, 4097, 3071, 1025, 1.5f, 0.5f, 16, ctx, dev, 10), 2.0 * 4097 * 3071 * 1025);
   report("sgemm_8192", gemm_case<float>(Layout::kColMajor, 8192, 8192, 8192, 1.5f, 0.5f, 16, ctx, dev, 5), 2.0 * 8192 * 8192 * 8192);

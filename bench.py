@@ -53,6 +53,10 @@ WORKLOADS = {
                        beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
     "sgemm_4096": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=4096, n=4096, k=4096, alpha=1.5,
                        beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
+    "sgemm_2048": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=2048, n=2048, k=2048, alpha=1.5,
+                       beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
+    "sgemm_1000": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=1000, n=1000, k=1000, alpha=1.5,
+                       beta=0.5, ld_pad=16, dist="uniform1", bound="fp32"),
     "sgemm_1024": dict(kind="gemm", precision=32, layout=ROW, ta=NO, tb=NO, m=1024, n=1024, k=1024, alpha=0.7,
                        beta=0.3, dist="uniform1", bound="fp32"),
     "sgemm_ragged": dict(kind="gemm", precision=32, layout=COL, ta=NO, tb=NO, m=4097, n=3071, k=1025, alpha=1.5,
